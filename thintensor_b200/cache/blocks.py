@@ -89,13 +89,20 @@ class BlockPool:
 class BlockTable:
     """The blocks of every live slot in one storage group, in logical order.  Entry
     ``i`` of a slot's row holds tokens ``i * block_tokens .. (i + 1) * block_tokens - 1``;
-    ``-1`` marks a block that a windowed group has already given back."""
+    ``-1`` marks a block that a windowed group has already given back.  With ``every`` above 1 the group keeps one
+    entry for each ``every`` tokens that are complete (entry n: tokens ``n * every .. n * every + every - 1``), and a
+    block holds ``block_tokens`` entries."""
 
-    def __init__(self, pool: BlockPool, block_tokens: int, window: int | None = None):
+    def __init__(self, pool: BlockPool, block_tokens: int, window: int | None = None, every: int = 1):
         self.pool = pool
         self.block_tokens = block_tokens
         self.window = window
+        self.every = max(1, int(every))
         self.rows: dict[int, list[int]] = {}
+
+    def blocks_for(self, tokens: int) -> int:
+        """Blocks that the entries of a sequence of ``tokens`` tokens fill."""
+        return -(-(tokens // self.every) // self.block_tokens)
 
     def open(self, slot: int) -> None:
         if slot in self.rows:
@@ -105,14 +112,14 @@ class BlockTable:
     def reserve(self, slot: int, tokens: int) -> bool:
         """Make room for positions 0..tokens-1; returns whether the row changed."""
         row = self.rows[slot]
-        need = -(-tokens // self.block_tokens)
+        need = self.blocks_for(tokens)
         if need <= len(row):
             return False
         row.extend(self.pool.alloc(need - len(row)))
         return True
 
     def blocks_needed(self, slot: int, tokens: int) -> int:
-        return max(0, -(-tokens // self.block_tokens) - len(self.rows[slot]))
+        return max(0, self.blocks_for(tokens) - len(self.rows[slot]))
 
     def trim(self, slot: int, length: int) -> bool:
         """For a windowed group: give back the blocks whose every token is older than

@@ -31,6 +31,7 @@ class KVGroup:
     runs: list[int]                 # schedule entries that own a cache in this group
     table: BlockTable
     storage: torch.Tensor | None    # [runs, blocks * kv_heads * BLOCK_TOKENS * (head_dim + value_dim)]: keys, then values
+    num_blocks: int = 0             # blocks of this group's pool
 
     def bytes(self) -> int:
         return 0 if self.storage is None else self.storage.numel() * self.storage.element_size()
@@ -52,6 +53,7 @@ class RunCache:
     v_pool: torch.Tensor | None     # [blocks, kv_heads, value_dim, BLOCK_TOKENS]
     writes: bool                    # False when the run reads another run's cache
     window: int | None
+    summary: "RunCache | None" = None   # the mixer's coarser cache (one entry for several tokens), where it keeps one
 
 
 class SequenceCache:
@@ -61,7 +63,9 @@ class SequenceCache:
     None) are what run ``i`` of the schedule asks for (a run with several mixers has an entry
     for each of them); ``cache_from[i]`` names the entry whose keys entry ``i`` reads instead
     of keeping its own.  ``num_blocks`` blocks of 64 tokens are shared by all
-    live sequences of a group; ``device=None`` keeps the bookkeeping only.
+    live sequences of a group; ``device=None`` keeps the bookkeeping only.  A group that keeps one entry for each
+    ``every`` tokens has ``ceil(num_blocks / every) + max_slots`` blocks of 64 entries: enough whenever the token
+    groups have room (a sequence of b token blocks fills at most ``ceil(b / every)`` of them).
     """
 
     def __init__(self, kv_needs: list[KVNeed | None], state_needs: list, cache_from: list[int | None],
@@ -86,7 +90,8 @@ class SequenceCache:
                 continue
             if need not in by_need:
                 by_need[need] = len(self.kv_groups)
-                self.kv_groups.append(KVGroup(need, [], BlockTable(BlockPool(self.num_blocks), BLOCK_TOKENS, need.window), None))
+                blocks = self.num_blocks if need.every <= 1 else -(-self.num_blocks // need.every) + self.max_slots
+                self.kv_groups.append(KVGroup(need, [], BlockTable(BlockPool(blocks), BLOCK_TOKENS, need.window, need.every), None, blocks))
             group = self.kv_groups[by_need[need]]
             self._run_group[run] = by_need[need]
             self._run_index[run] = len(group.runs)
@@ -97,7 +102,7 @@ class SequenceCache:
             if kv_needs[run] is None or kv_needs[source] is None:
                 raise CacheError(f"run {run} reads the cache of run {source}, but one of them keeps no keys")
             a, b = kv_needs[run], kv_needs[source]
-            if (a.kv_heads, a.head_dim, a.v_dim) != (b.kv_heads, b.head_dim, b.v_dim):
+            if (a.kv_heads, a.head_dim, a.v_dim, a.every) != (b.kv_heads, b.head_dim, b.v_dim, b.every):
                 raise CacheError(f"run {run} reads the cache of run {source}, whose key/value shape differs")
             if b.window is not None and (a.window is None or a.window > b.window):
                 # the source's group gives blocks back by the source's window; a reader that looks
@@ -121,7 +126,7 @@ class SequenceCache:
         if self.device is not None:
             for group in self.kv_groups:
                 per_block = group.need.kv_heads * BLOCK_TOKENS
-                shape = (len(group.runs), self.num_blocks * per_block * (group.need.head_dim + group.need.v_dim))
+                shape = (len(group.runs), group.num_blocks * per_block * (group.need.head_dim + group.need.v_dim))
                 # zeros, not empty: a tensor-core product multiplies the unused tail of a block by a
                 # probability of exactly zero, which must not meet a NaN left in fresh memory
                 group.storage = torch.zeros(shape, dtype=dtype, device=self.device)
@@ -154,7 +159,7 @@ class SequenceCache:
     # --------------------------------------------------------------- blocks
     def blocks_needed(self, slot: int, total_tokens: int) -> int:
         """Blocks (summed over groups, the worst group counted) that ``reserve`` would take."""
-        return max((g.table.blocks_needed(slot, total_tokens) for g in self.kv_groups), default=0)
+        return max((g.table.blocks_needed(slot, total_tokens) for g in self.kv_groups if g.need.every <= 1), default=0)
 
     def reserve(self, slot: int, total_tokens: int) -> None:
         """Make room for the sequence to grow to ``total_tokens`` tokens."""
@@ -194,9 +199,9 @@ class SequenceCache:
         k = v = None
         if g.storage is not None:
             need = g.need
-            keys = self.num_blocks * need.kv_heads * BLOCK_TOKENS * need.head_dim
-            k = g.storage[index, :keys].view(self.num_blocks, need.kv_heads, BLOCK_TOKENS, need.head_dim)
-            v = g.storage[index, keys:].view(self.num_blocks, need.kv_heads, need.v_dim, BLOCK_TOKENS)
+            keys = g.num_blocks * need.kv_heads * BLOCK_TOKENS * need.head_dim
+            k = g.storage[index, :keys].view(g.num_blocks, need.kv_heads, BLOCK_TOKENS, need.head_dim)
+            v = g.storage[index, keys:].view(g.num_blocks, need.kv_heads, need.v_dim, BLOCK_TOKENS)
         return RunCache(group, k, v, self._cache_from[run] is None, g.need.window)
 
     def run_state(self, run: int) -> list[torch.Tensor]:
@@ -218,4 +223,4 @@ class SequenceCache:
 
     @property
     def free_blocks(self) -> int:
-        return min((g.table.pool.free_count for g in self.kv_groups), default=self.num_blocks)
+        return min((g.table.pool.free_count for g in self.kv_groups if g.need.every <= 1), default=self.num_blocks)

@@ -502,8 +502,13 @@ extern "C" int tt_rope_append(const float* qkv, int splits, long long split_stri
 //         (head_dim numbers per q and k head, value_dim per v head).
 //   norm: q_norm / k_norm (float32 [head_dim], or null for none) multiply x / sqrt(mean(x^2) + norm_eps) per head,
 //         before the rotation.
+//         unit_norm != 0: both are normalised without a weight.
+//   query gain: with q_gain_every > 0 the queries at position p are multiplied, after their norm, by
+//         1 + q_gain_coef * ln(floor((p + 1) / q_gain_every) + 1)   (float32).
 //   rotation of the first rotary_dim numbers of a head by angle inv_freq[i] * float(position):
 //         interleaved != 0 pairs (2i, 2i + 1), else (i, i + rotary_dim / 2).
+//   value_from_keys != 0: the projection has no value columns; a value head is its key head before the norm
+//         (value_dim == head_dim).
 // One warp per (token, head); the head's numbers pass through the warp's piece of shared memory.
 // ------------------------------------------------------------------------------------
 constexpr int QK_WARPS = 4;
@@ -517,6 +522,7 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
                                            int pool_blocks, const int* __restrict__ cu, const int* __restrict__ len_before,
                                            int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
                                            int write_cache, const float2* __restrict__ cos_sin, const int2* __restrict__ where,
+                                           int unit_norm, float q_gain_coef, int q_gain_every, int value_from_keys,
                                            unsigned* status) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
@@ -537,8 +543,9 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
         const int kh = item - heads - kv_heads;
         const long long off = tt_value_offset(table_row, pos, kh, kv_heads, value_dim, pool_blocks, status);
         if (off < 0) return;
+        const float* from = value_from_keys ? row + q_cols + kh * head_dim : row + q_cols + k_cols + kh * value_dim;
         for (int d = lane; d < value_dim; d += 32)
-            v_pool[off + (long long)d * TT_BLOCK_TOKENS] = tt_from_float<TAct>(sum_slices(row + q_cols + k_cols + kh * value_dim + d, splits, split_stride));
+            v_pool[off + (long long)d * TT_BLOCK_TOKENS] = tt_from_float<TAct>(sum_slices(from + d, splits, split_stride));
         return;
     }
     const bool is_q = item < heads;
@@ -552,10 +559,12 @@ __global__ void qk_norm_rope_append_kernel(const float* __restrict__ proj, int s
         x[d] = v;
         sumsq += v * v;
     }
-    if (norm) {
-        const float r = rsqrtf(tt_warp_sum(sumsq) / (float)head_dim + norm_eps);
+    if (norm || unit_norm || (is_q && q_gain_every > 0)) {
+        float r = 1.0f;
+        if (norm || unit_norm) r = rsqrtf(tt_warp_sum(sumsq) / (float)head_dim + norm_eps);
+        if (is_q && q_gain_every > 0) r *= 1.0f + q_gain_coef * logf((float)((pos + 1) / q_gain_every + 1));
         __syncwarp();
-        for (int d = lane; d < head_dim; d += 32) x[d] = x[d] * r * __ldg(norm + d);
+        for (int d = lane; d < head_dim; d += 32) x[d] = x[d] * r * (norm ? __ldg(norm + d) : 1.0f);
     }
     __syncwarp();
     TAct* dst;
@@ -586,20 +595,22 @@ extern "C" int tt_qk_norm_rope_append(const float* proj, int splits, long long s
                                       float attention_scaling, void* q_out, void* k_pool, void* v_pool, int act_dtype,
                                       const int* table, int table_width, int pool_blocks, const int* cu, const int* len_before,
                                       int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
-                                      int write_cache, const void* cos_sin_table, const void* where_table, unsigned* status,
+                                      int write_cache, const void* cos_sin_table, const void* where_table, int unit_norm,
+                                      float q_gain_coef, int q_gain_every, int value_from_keys, unsigned* status,
                                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const float2* cos_sin = (const float2*)cos_sin_table;        // both or neither: the step's rope table
     const int2* where = (const int2*)where_table;
     if ((cos_sin == nullptr) != (where == nullptr)) return (int)cudaErrorInvalidValue;
     if (rotary_dim < 0 || rotary_dim % 2 || rotary_dim > head_dim || head_dim <= 0 || value_dim <= 0) return (int)cudaErrorInvalidValue;
+    if (value_from_keys && value_dim != head_dim) return (int)cudaErrorInvalidValue;
     const long long warps = (long long)n_tokens * (heads + (write_cache ? 2 * kv_heads : 0));
     const unsigned blocks = (unsigned)((warps + QK_WARPS - 1) / QK_WARPS);
     const size_t shared = (size_t)QK_WARPS * (head_dim > value_dim ? head_dim : value_dim) * sizeof(float);
     if (act_dtype == TT_F32)
-        tt_launch_pdl(qk_norm_rope_append_kernel<float>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, status);
+        tt_launch_pdl(qk_norm_rope_append_kernel<float>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (float*)q_out, (float*)k_pool, (float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, unit_norm, q_gain_coef, q_gain_every, value_from_keys, status);
     else
-        tt_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, status);
+        tt_launch_pdl(qk_norm_rope_append_kernel<__nv_bfloat16>, dim3(blocks), dim3(QK_WARPS * 32), shared, stream, proj, splits, (size_t)split_stride, cols, q_norm, k_norm, norm_eps, inv_freq, rotary_dim, interleaved, attention_scaling, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, write_cache, cos_sin, where, unit_norm, q_gain_coef, q_gain_every, value_from_keys, status);
     TT_LAUNCH_CHECK();
 }
 
@@ -815,5 +826,179 @@ extern "C" int tt_token_shift(const void* x, int dtype, const float* mix, float*
         tt_launch_pdl(token_shift_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)x, mix, state, (float*)out, cu, slots, sequences, hidden);
     else
         tt_launch_pdl(token_shift_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)x, mix, state, (__nv_bfloat16*)out, cu, slots, sequences, hidden);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// embedding with a learned position vector:
+//   residual[t, :] = table[token[t], :] * scale + positions[p, :],  p = len_before[b] + (t - cu[b])   (float32 out)
+// A token outside the table, or a position beyond the position table's rows, raises the bad-token bit and leaves zeros.
+// ------------------------------------------------------------------------------------
+template <typename TW>
+__global__ void embed_position_gather_kernel(const TW* __restrict__ table, const TW* __restrict__ positions,
+                                             const int* __restrict__ tokens, const int* __restrict__ cu,
+                                             const int* __restrict__ len_before, int sequences, float* __restrict__ residual,
+                                             int hidden, int vocab, int max_positions, float scale, unsigned* status) {
+    tt_pdl_wait();                      // the first kernel of a step: see embed_gather_kernel
+    tt_pdl_launch_dependents();
+    const int t = blockIdx.x;
+    const int id = tokens[t];
+    const int b = tt_find_sequence(cu, sequences, t);
+    const int pos = len_before[b] + (t - cu[b]);
+    float* out = residual + (size_t)t * hidden;
+    if (id < 0 || id >= vocab || pos < 0 || pos >= max_positions) {
+        if (threadIdx.x == 0) atomicOr(status, TT_STATUS_BAD_TOKEN);
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[j] = 0.0f;
+        return;
+    }
+    const TW* row = table + (size_t)id * hidden;
+    const TW* prow = positions + (size_t)pos * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+        out[j] = tt_to_float(row[j]) * scale + tt_to_float(prow[j]);
+}
+
+extern "C" int tt_embed_position_gather(const void* table, const void* positions, int table_dtype, const int* tokens, const int* cu,
+                                        const int* len_before, int sequences, float* residual, int n_tokens, int hidden, int vocab,
+                                        int max_positions, float scale, unsigned* status, cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == TT_F32)
+        tt_launch_pdl(embed_position_gather_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)table, (const float*)positions, tokens, cu, len_before, sequences, residual, hidden, vocab, max_positions, scale, status);
+    else
+        tt_launch_pdl(embed_position_gather_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)table, (const __nv_bfloat16*)positions, tokens, cu, len_before, sequences, residual, hidden, vocab, max_positions, scale, status);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// Ungated activation: act[t, j] = f(sum over slices of x[s][t, j]).  f by `activation`: 0 silu, 1 relu, 2 tanh-gelu (as
+// in tt_gate_activation), 3 xielu with two numbers a = softplus(p) and c = 1/2 + softplus(q) that the caller has formed:
+//   z > 0: a z^2 + z / 2;   z <= 0: c (exp(z) - 1 - z) + z / 2     (expm1f keeps small z exact)
+// ------------------------------------------------------------------------------------
+__device__ __forceinline__ float tt_unary_activation(float z, int activation, float a, float c) {
+    if (activation == 3) return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(c, expm1f(z) - z, 0.5f * z);
+    return tt_gate_activation(z, activation);
+}
+
+template <typename TAct>
+__global__ void activation_kernel(const float* __restrict__ x, int splits, size_t split_stride, TAct* __restrict__ act,
+                                  size_t total, int activation, float a, float c) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const size_t idx = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (idx >= total) return;
+    if (idx + 4 <= total && (split_stride & 3) == 0) {
+        float4 z = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s = 0; s < splits; ++s) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(x + s * split_stride + idx));
+            z.x += v.x; z.y += v.y; z.z += v.z; z.w += v.w;
+        }
+        tt_store4(act + idx, tt_unary_activation(z.x, activation, a, c), tt_unary_activation(z.y, activation, a, c),
+                  tt_unary_activation(z.z, activation, a, c), tt_unary_activation(z.w, activation, a, c));
+        return;
+    }
+    for (size_t i = idx; i < total && i < idx + 4; ++i) {
+        float z = 0.0f;
+        for (int s = 0; s < splits; ++s) z += __ldg(x + s * split_stride + i);
+        act[i] = tt_from_float<TAct>(tt_unary_activation(z, activation, a, c));
+    }
+}
+
+extern "C" int tt_activation(const float* x, int splits, long long split_stride, void* act, int act_dtype, long long total,
+                             int activation, float a, float c, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (activation < 0 || activation > 3 || (total & 3)) return (int)cudaErrorInvalidValue;     // rows of whole groups of four
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total / 4 + threads - 1) / threads);
+    if (act_dtype == TT_F32)
+        tt_launch_pdl(activation_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, splits, (size_t)split_stride, (float*)act, (size_t)total, activation, a, c);
+    else
+        tt_launch_pdl(activation_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, x, splits, (size_t)split_stride, (__nv_bfloat16*)act, (size_t)total, activation, a, c);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// The residual addition and RMSNorm of add_rmsnorm_kernel with two more steps on the way, all float32:
+//   v = delta[0][r] + delta[1][r] + ...                                        (fixed order; no delta: v = 0)
+//   post_weight:  v = v * rsqrt(mean(v^2) + post_eps) * (post_weight + post_offset)     (the norm after a sublayer)
+//   x = residual[r] + v
+//   results:      results[index][r] = x;  with depth_weights: x = sum_{j <= index} depth_weights[j] * results[j][r]
+//                 (result `index` is taken from the registers; the sum runs from j = 0 upwards)
+//   residual[r] = x                                                            (only when rows == nullptr)
+//   out[i] = x * rsqrt(mean(x^2) + eps) * (weight + weight_offset)
+// With `rows`, output row i comes from row rows[i] and neither the stream nor the results are written.
+// One block per output row; every thread keeps its numbers of the row in registers (PIECES float4 pieces when the
+// width is a multiple of four and at most 16384, else the row passes through shared memory).
+// ------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_chain_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
+                         const float* __restrict__ post_weight, float post_offset, float post_eps,
+                         float* __restrict__ results, size_t result_stride, int index, const float* __restrict__ depth_weights,
+                         const float* __restrict__ weight, float weight_offset, float eps, TOut* __restrict__ out,
+                         const int* __restrict__ rows, int hidden) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    extern __shared__ float chain_shared[];     // hidden floats (the row), then 32 for the reductions
+    float* rowbuf = chain_shared;
+    float* reduce = chain_shared + hidden;
+    const int i = blockIdx.x;
+    const int r = rows ? rows[i] : i;
+    float* res = residual + (size_t)r * hidden;
+    // 1. the delta's slices, summed, and their mean square
+    float sumsq = 0.0f;
+    if (delta) {
+        const float* del = delta + (size_t)r * hidden;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+            float v = 0.0f;
+            for (int s = 0; s < splits; ++s) v += __ldg(del + (size_t)s * split_stride + j);
+            rowbuf[j] = v;
+            sumsq += v * v;
+        }
+    } else {
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) rowbuf[j] = 0.0f;
+    }
+    float gain = 1.0f;
+    if (post_weight) gain = rsqrtf(tt_block_sum(sumsq, reduce) / (float)hidden + post_eps);
+    // 2. into the stream, kept as a result, mixed with the earlier results; every thread revisits its own numbers only
+    sumsq = 0.0f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = rowbuf[j];
+        if (post_weight) v = v * gain * (__ldg(post_weight + j) + post_offset);
+        float x = res[j] + v;
+        if (results) {
+            const float* mine = results + (size_t)r * hidden + j;
+            if (!rows) results[(size_t)index * result_stride + (size_t)r * hidden + j] = x;
+            if (depth_weights) {
+                float mixed = 0.0f;
+                for (int k = 0; k < index; ++k) mixed = fmaf(__ldg(depth_weights + k), mine[(size_t)k * result_stride], mixed);
+                x = fmaf(__ldg(depth_weights + index), x, mixed);
+            }
+        }
+        if (!rows) res[j] = x;
+        rowbuf[j] = x;
+        sumsq += x * x;
+    }
+    const float rstd = rsqrtf(tt_block_sum(sumsq, reduce) / (float)hidden + eps);
+    TOut* o = out + (size_t)i * hidden;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
+        o[j] = tt_from_float<TOut>(rowbuf[j] * rstd * (__ldg(weight + j) + weight_offset));
+}
+
+extern "C" int tt_add_rmsnorm_chain(float* residual, const float* delta, int splits, long long split_stride, const float* post_weight,
+                                    float post_offset, float post_eps, float* results, long long result_stride, int index,
+                                    const float* depth_weights, const float* weight, float weight_offset, float eps, void* out,
+                                    int out_dtype, const int* rows, int n_rows, int hidden, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0 || index < 0 || (depth_weights && !results)) return (int)cudaErrorInvalidValue;
+    int threads = hidden >= 4096 ? 1024 : hidden >= 1024 ? 512 : hidden >= 256 ? 256 : 128;
+    const size_t shared = ((size_t)hidden + 32) * sizeof(float);
+    if (shared > 200 * 1024) return (int)cudaErrorInvalidValue;
+    if (out_dtype == TT_F32) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_chain_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        tt_launch_pdl(add_rmsnorm_chain_kernel<float>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, post_weight, post_offset, post_eps, results, (size_t)result_stride, index, depth_weights, weight, weight_offset, eps, (float*)out, rows, hidden);
+    } else {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_chain_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        tt_launch_pdl(add_rmsnorm_chain_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, post_weight, post_offset, post_eps, results, (size_t)result_stride, index, depth_weights, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
+    }
     TT_LAUNCH_CHECK();
 }

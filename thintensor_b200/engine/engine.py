@@ -94,6 +94,7 @@ class Engine:
         self.status = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._staging = _Staging()
         self.vocab_size = model.spec.vocab_size
+        self.max_positions = getattr(model.embedding.part, "max_positions", None)   # an embedding with a learned vector per position has so many
         self.launch_count = 0
         self.decode_states: dict = {}        # the generation loop's captured decode steps, by shape
         # Steps through `step` of a shape that has run before are replayed from a CUDA graph: everything that
@@ -123,7 +124,10 @@ class Engine:
             if entry.slot in seen:
                 raise StepError(f"slot {entry.slot} appears twice in one step")
             seen.add(entry.slot)
-            self.cache.length(entry.slot)  # raises if the slot is not live
+            held = self.cache.length(entry.slot)  # raises if the slot is not live
+            if self.max_positions is not None and held + len(entry.tokens) > self.max_positions:
+                raise StepError(f"slot {entry.slot} would grow to {held + len(entry.tokens)} tokens, but the model has position vectors "
+                                f"for {self.max_positions}")
             if len(entry.tokens) == 0:
                 raise StepError(f"slot {entry.slot} brings no tokens")
             try:

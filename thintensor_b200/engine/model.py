@@ -109,6 +109,7 @@ class DecoderModel:
         sets ``self.users``: for each run, the entries of its mixers."""
         kv, state, source = [], [], []
         self.users: list[list[int]] = []
+        self.summaries: dict[int, int] = {}         # a mixer's entry -> the entry of its coarser cache
         for run in self.spec.schedule:
             mixers = self.layers[run.layer].mixers()
             own = list(self.layers[run.layer].state_needs())        # states of the arrangement itself: one more entry behind the mixers'
@@ -124,6 +125,16 @@ class DecoderModel:
             if own:
                 kv.append(None)
                 state.append(own)
+                source.append(None)
+            for i, mixer in enumerate(mixers):              # coarser caches (block means, say) follow as entries of their own
+                coarse = mixer.summary_need()
+                if coarse is None:
+                    continue
+                if run.cache_from is not None:
+                    raise ValueError(f"a run of layer {run.layer} reads another run's cache, but its mixer keeps a summary of its own")
+                self.summaries[mine[i]] = len(kv)
+                kv.append(coarse)
+                state.append([])
                 source.append(None)
             self.users.append(mine)
         # the embedding's states (the previous token, say) are the last entry
@@ -141,6 +152,12 @@ class DecoderModel:
         where = self.device if device == "default" else device
         return SequenceCache(kv, state, source, num_blocks, max_slots, self.dtype, where)
 
+    def _run_cache(self, cache: SequenceCache, entry: int):
+        view = cache.run_cache(entry)
+        if entry in self.summaries:
+            view.summary = cache.run_cache(self.summaries[entry])
+        return view
+
     # ------------------------------------------------------------------ forward
     def forward(self, ctx: StepContext, cache: SequenceCache, rows: torch.Tensor | None) -> torch.Tensor | None:
         """Run the packed tokens of ``ctx`` through the schedule and return float32
@@ -154,7 +171,7 @@ class DecoderModel:
         pending: Delta | None = None
         for index, run in enumerate(self.spec.schedule):
             users = self.users[index]
-            pending = self.layers[run.layer].run(ctx, residual, pending, [cache.run_cache(u) for u in users], [cache.run_state(u) for u in users])
+            pending = self.layers[run.layer].run(ctx, residual, pending, [self._run_cache(cache, u) for u in users], [cache.run_state(u) for u in users])
         if rows is None:
             return None
         wanted = ctx.scratch("model.final", (rows.numel(), self.spec.hidden_size))

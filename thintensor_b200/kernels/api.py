@@ -166,6 +166,22 @@ def embed_gather(table: torch.Tensor, tokens: torch.Tensor, residual: torch.Tens
     _check(fn(_ptr(table), dtype_code(table.dtype), _ptr(tokens), _ptr(residual), n, hidden, table.shape[0], scale, _ptr(status), _stream()), "embed_gather")
 
 
+def embed_position_gather(table: torch.Tensor, positions: torch.Tensor, tokens: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor,
+                          sequences: int, residual: torch.Tensor, scale: float, status: torch.Tensor) -> None:
+    """residual[t] = table[tokens[t]] * scale + positions[p] with p the position of packed token t in its sequence."""
+    _need(tokens, torch.int32, "tokens")
+    _need(residual, torch.float32, "residual")
+    if not table.is_contiguous() or not positions.is_contiguous() or table.dtype != positions.dtype:
+        raise KernelError("embedding tables must be contiguous and of one dtype")
+    if positions.shape[1] != table.shape[1]:
+        raise KernelError(f"the position table must have rows of {table.shape[1]} numbers, got {tuple(positions.shape)}")
+    n, hidden = tokens.numel(), table.shape[1]
+    fn = _fn("elementwise", "tt_embed_position_gather", [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                         c_int, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(table), _ptr(positions), dtype_code(table.dtype), _ptr(tokens), _ptr(cu), _ptr(len_before), sequences, _ptr(residual), n,
+              hidden, table.shape[0], positions.shape[0], scale, _ptr(status), _stream()), "embed_position_gather")
+
+
 def embed_pair_gather(table: torch.Tensor, pair_table: torch.Tensor, tokens: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor,
                       sequences: int, last_token: torch.Tensor, residual: torch.Tensor, buckets: int, mul_prev: int, mul_cur: int,
                       scale: float, status: torch.Tensor) -> None:
@@ -224,6 +240,47 @@ def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torc
     _check(fn(_ptr(residual), _ptr(delta), splits, stride, _ptr(weight), weight_offset, eps, _ptr(out), dtype_code(out.dtype), _ptr(rows), n_rows, hidden, _stream()), "add_rmsnorm")
 
 
+def add_rmsnorm_chain(residual: torch.Tensor, delta: torch.Tensor | None, post_weight: torch.Tensor | None, post_offset: float, post_eps: float,
+                      results: torch.Tensor | None, index: int, depth_weights: torch.Tensor | None, weight: torch.Tensor, weight_offset: float,
+                      eps: float, out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
+    """:func:`add_rmsnorm` with two more steps on the way.  The summed delta is first normalised,
+    ``v * rsqrt(mean(v^2) + post_eps) * (post_weight + post_offset)`` (``post_weight`` None: added as it is).  After the
+    addition the stream is kept as ``results[index]`` (float32 ``[count, tokens, hidden]``) and, with ``depth_weights``
+    (float32, at least ``index + 1`` numbers), replaced by ``sum(depth_weights[j] * results[j] for j <= index)``.  With
+    ``rows`` nothing but ``out`` is written."""
+    _need(residual, torch.float32, "residual")
+    _need(weight, torch.float32, "norm weight")
+    if not out.is_contiguous():
+        raise KernelError("norm output must be contiguous")
+    hidden = residual.shape[-1]
+    splits, stride = 0, 0
+    if delta is not None:
+        _need(delta, torch.float32, "delta")
+        splits, stride = delta.shape[0], delta.stride(0)
+    if post_weight is not None:
+        _need(post_weight, torch.float32, "norm weight of the delta")
+        if delta is None:
+            raise KernelError("a norm of the delta needs a delta")
+    result_stride = 0
+    if results is not None:
+        _need(results, torch.float32, "results")
+        if results.dim() != 3 or tuple(results.shape[1:]) != tuple(residual.shape) or not 0 <= index < results.shape[0]:
+            raise KernelError(f"results must be [count > {index}, {residual.shape[0]}, {hidden}], got {tuple(results.shape)}")
+        result_stride = results.stride(0)
+    if depth_weights is not None:
+        _need(depth_weights, torch.float32, "depth weights")
+        if results is None or depth_weights.numel() < index + 1:
+            raise KernelError(f"mixing results 0..{index} needs the results and {index + 1} weights")
+    n_rows = rows.numel() if rows is not None else residual.shape[0]
+    if rows is not None:
+        _need(rows, torch.int32, "rows")
+    fn = _fn("elementwise", "tt_add_rmsnorm_chain", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_float, c_float, c_void_p, c_longlong, c_int,
+                                                     c_void_p, c_void_p, c_float, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(residual), _ptr(delta), splits, stride, _ptr(post_weight), post_offset, post_eps, _ptr(results), result_stride, index,
+              _ptr(depth_weights), _ptr(weight), weight_offset, eps, _ptr(out), dtype_code(out.dtype), _ptr(rows), n_rows, hidden, _stream()),
+           "add_rmsnorm_chain")
+
+
 def add_layernorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, bias: torch.Tensor | None, eps: float,
                   out: torch.Tensor, rows: torch.Tensor | None = None) -> None:
     """residual += sum(delta over its first axis); out = (x - mean) / sqrt(var + eps) * weight (+ bias), the
@@ -251,17 +308,25 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
                         k_pool: torch.Tensor | None, v_pool: torch.Tensor | None, table: torch.Tensor, cu: torch.Tensor,
                         len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
                         value_dim: int, status: torch.Tensor, cos_sin: torch.Tensor | None = None,
-                        where: torch.Tensor | None = None) -> None:
+                        where: torch.Tensor | None = None, unit_norm: bool = False, q_gain: tuple[float, int] | None = None,
+                        value_from_keys: bool = False) -> None:
     """The general form of :func:`rope_append`: float32 partial sums ``proj`` [splits, tokens, cols] hold q heads, then k
     heads (``head_dim`` numbers each), then v heads (``value_dim`` each).  q and k are normalised per head (x / rms(x) *
     weight; ``q_norm`` / ``k_norm`` float32 [head_dim] or None), then their first ``rotary_dim`` numbers are rotated, in
     neighbouring pairs (``interleaved``) or in halves; q goes to ``q_out``, k and v to the block pools.  Without pools
     the projection holds queries only.  ``cos_sin`` and ``where``: the step's :func:`rope_table` for this layer's
-    frequencies, looked up instead of computing positions, cosines and sines per head."""
+    frequencies, looked up instead of computing positions, cosines and sines per head.  ``unit_norm``: q and k are
+    normalised without a weight.  ``q_gain`` = (coef, every): queries at position p are multiplied by
+    ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``value_from_keys``: the projection has no v heads; a value head is its
+    key head before the norm."""
     _need(proj, torch.float32, "projection")
     _need(inv_freq, torch.float32, "inv_freq")
     write = k_pool is not None
-    cols = heads * head_dim + (kv_heads * (head_dim + value_dim) if write else 0)
+    if value_from_keys and value_dim != head_dim:
+        raise KernelError("values that are the keys have the keys' size")
+    if q_gain is not None and int(q_gain[1]) < 1:
+        raise KernelError("the query gain's period must be at least one position")
+    cols = heads * head_dim + (kv_heads * (head_dim + (0 if value_from_keys else value_dim)) if write else 0)
     if proj.shape[-1] != cols:
         raise KernelError(f"the projection has {proj.shape[-1]} columns, expected {cols}")
     for norm in (q_norm, k_norm):
@@ -282,11 +347,13 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
             raise KernelError("the rope table does not fit the step")
     fn = _fn("elementwise", "tt_qk_norm_rope_append", [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                       c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_int,
+                                                       c_int, c_void_p, c_void_p])
     _check(fn(_ptr(proj), proj.shape[0], proj.stride(0), cols, _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(inv_freq), rotary_dim,
               1 if interleaved else 0, attention_scaling, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), dtype_code(q_out.dtype), _ptr(table),
               table.shape[1], k_pool.shape[0] if write else 0, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim,
-              value_dim, 1 if write else 0, _ptr(cos_sin), _ptr(where), _ptr(status), _stream()), "qk_norm_rope_append")
+              value_dim, 1 if write else 0, _ptr(cos_sin), _ptr(where), 1 if unit_norm else 0, 0.0 if q_gain is None else float(q_gain[0]),
+              0 if q_gain is None else int(q_gain[1]), 1 if value_from_keys else 0, _ptr(status), _stream()), "qk_norm_rope_append")
 
 
 def rope_append(qkv: torch.Tensor, inv_freq: torch.Tensor, rotary_dim: int, attention_scaling: float, q_out: torch.Tensor,
@@ -341,6 +408,22 @@ def swiglu(gate_up: torch.Tensor, act: torch.Tensor, activation: str = "silu") -
               GATE_ACTIVATIONS[activation], _stream()), "swiglu")
 
 
+UNARY_ACTIVATIONS = {**GATE_ACTIVATIONS, "xielu": 3}
+
+
+def activation(x: torch.Tensor, act: torch.Tensor, activation: str = "gelu_tanh", a: float = 0.0, c: float = 0.0) -> None:
+    """act = f(sum of the float32 slices ``x`` [splits, tokens, inter]) in the activation dtype.  ``xielu`` takes the two
+    numbers a = softplus(p) and c = 1 / 2 + softplus(q): ``a z^2 + z / 2`` for z > 0, ``c (exp(z) - 1 - z) + z / 2`` otherwise."""
+    _need(x, torch.float32, "the activation's input")
+    if x.dim() != 3 or tuple(act.shape) != tuple(x.shape[1:]) or not act.is_contiguous():
+        raise KernelError("activation: the output must be contiguous [tokens, inter] for an input [splits, tokens, inter]")
+    if x.shape[2] % 4:
+        raise KernelError("activation: rows must be whole groups of four numbers")
+    fn = _fn("elementwise", "tt_activation", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_float, c_float, c_void_p])
+    _check(fn(_ptr(x), x.shape[0], x.stride(0), _ptr(act), dtype_code(act.dtype), act.numel(), UNARY_ACTIVATIONS[activation], a, c, _stream()),
+           "activation")
+
+
 def copy_int32(dst: torch.Tensor, src: torch.Tensor, extra: torch.Tensor | None = None) -> None:
     """dst[:n] = src for small int32 vectors; either side may be pinned host memory.  With ``extra``
     (one int32 on the device, the status word say) ``dst`` has n + 1 entries and dst[n] = extra[0]."""
@@ -390,6 +473,71 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu),
               _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, _ptr(sinks), window, splits, _ptr(out),
               _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
+
+
+def differential_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
+                           len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, dim: int, value_dim: int,
+                           scale: float, lam: float, gain: float, eps: float, splits: int, out: torch.Tensor,
+                           part_acc: torch.Tensor | None, part_ml: torch.Tensor | None, status: torch.Tensor) -> None:
+    """Causal differential attention over the block cache: query rows ``[tokens, heads, 2 * dim]`` and cached key rows of
+    ``2 * dim`` numbers hold two maps; ``out[t, h] = norm(a1 - lam * a2) * gain`` with a1, a2 the two maps' softmax
+    attentions over the same values (``value_dim`` numbers a head) and norm the division by ``sqrt(mean(o^2) + eps)``.
+    ``part_acc`` / ``part_ml`` (float32, ``tokens * heads * splits * 2 * value_dim`` and ``... * 4`` numbers) for splits > 1."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+        raise KernelError("queries, cache and output must share a dtype")
+    if k_pool.shape[-1] != 2 * dim or q.shape[-1] != heads * 2 * dim:
+        raise KernelError("differential attention: rows of queries and keys hold two maps of dim numbers")
+    if splits > 1:
+        _need(part_acc, torch.float32, "partial accumulators")
+        _need(part_ml, torch.float32, "partial maxima and sums")
+        if part_acc.numel() < n_tokens * heads * splits * 2 * value_dim or part_ml.numel() < n_tokens * heads * splits * 4:
+            raise KernelError("differential attention: scratch for the slices is too small")
+    fn = _fn("attention_forms", "tt_differential_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
+                                                              c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_int, c_void_p,
+                                                              c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before),
+              sequences, n_tokens, heads, kv_heads, dim, value_dim, scale, lam, gain, eps, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml),
+              _ptr(status), _stream()), "differential_attention", 2 if splits > 1 else 1)
+
+
+def pool_blocks(k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, mean_k: torch.Tensor, mean_v: torch.Tensor,
+                mean_table: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor, sequences: int, most_blocks: int, kv_heads: int,
+                head_dim: int, value_dim: int, every: int, status: torch.Tensor) -> None:
+    """For every block of ``every`` tokens that this step completes (tokens ``n * every .. n * every + every - 1`` with the last
+    one among the step's), the mean of the block's cached keys and the mean of its cached values, written as entry n of
+    the coarser cache ``mean_k`` / ``mean_v`` (laid out like the token pools, addressed through ``mean_table``).
+    ``most_blocks`` bounds the blocks one sequence can complete in the step."""
+    if mean_k.dtype != k_pool.dtype or mean_v.dtype != k_pool.dtype:
+        raise KernelError("the token cache and the coarser cache must share a dtype")
+    fn = _fn("attention_forms", "tt_pool_blocks", [c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+    _check(fn(_ptr(k_pool), _ptr(v_pool), dtype_code(k_pool.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(mean_k), _ptr(mean_v),
+              _ptr(mean_table), mean_table.shape[1], mean_k.shape[0], _ptr(cu), _ptr(len_before), sequences, most_blocks, kv_heads, head_dim,
+              value_dim, every, _ptr(status), _stream()), "pool_blocks")
+
+
+def pooled_window_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, mean_k: torch.Tensor,
+                            mean_v: torch.Tensor, mean_table: torch.Tensor, every: int, cu: torch.Tensor, len_before: torch.Tensor,
+                            sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int, scale: float, cap: float, window: int,
+                            splits: int, out: torch.Tensor, part_acc: torch.Tensor | None, part_ml: torch.Tensor | None,
+                            status: torch.Tensor) -> None:
+    """Attention of position i over the keys ``i - window < j <= i`` and, in the same softmax, over entry n of the coarser
+    cache for every block of ``every`` tokens with ``n * every + every - 1 <= i - window``; ``cap`` > 0 caps the scores,
+    ``cap * tanh(s / cap)``.  Values have the keys' size."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype or mean_k.dtype != q.dtype or mean_v.dtype != q.dtype:
+        raise KernelError("queries, caches and output must share a dtype")
+    if splits > 1:
+        _need(part_acc, torch.float32, "partial accumulators")
+        _need(part_ml, torch.float32, "partial maxima and sums")
+        if part_acc.numel() < n_tokens * heads * splits * head_dim or part_ml.numel() < n_tokens * heads * splits * 2:
+            raise KernelError("pooled window attention: scratch for the slices is too small")
+    fn = _fn("attention_forms", "tt_pooled_window_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
+                                                               c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                               c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+    _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(mean_k), _ptr(mean_v),
+              _ptr(mean_table), mean_table.shape[1], mean_k.shape[0], every, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads,
+              head_dim, scale, cap, window, splits, _ptr(out), _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()),
+           "pooled_window_attention", 2 if splits > 1 else 1)
 
 
 def _attention_launches(splits: int, decode: bool, tickets: bool = False) -> int:

@@ -34,6 +34,7 @@ SOURCES: dict[str, list[str]] = {
     "sampling": [],
     "attention_static_scratch": [],
     "gemm_tcgen05": [],
+    "attention_forms": [],
     "attention_mma": [],
     "attention_tcgen05": [],
     "recurrent": [],

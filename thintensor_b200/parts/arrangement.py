@@ -7,13 +7,19 @@ layer's second addition is done by the following layer's first norm (or by the f
 norm).  For long prompts the output projections add their product into the stream themselves
 (their tensor-core kernel's epilogue reads and writes the tile once, which spares the
 norm kernel a read of the product and a write of the stream); the delta is then empty.
+
+``sandwich``: every sublayer stands between two norms, ``h += norm_after(mixer(norm_before(h)))`` and the same for the
+feed-forward, and the layer's end may mix the results of all layers so far into the stream that goes on.  The norm
+after a sublayer and the mixing are not kernels of their own: the delta that the sublayer hands on says what is to be
+done with it, and the next norm's kernel does it on its way (the layer's last delta reaches the next layer's first
+norm, or the final norm).
 """
 from __future__ import annotations
 
 import torch
 
 from ..kernels import api
-from .base import ARRANGEMENTS, Arrangement, Delta
+from .base import ARRANGEMENTS, Arrangement, Delta, DepthStep
 
 
 @ARRANGEMENTS.register("pre_norm")
@@ -123,3 +129,52 @@ class Parallel(Arrangement):
         both = ctx.scratch("block.pair", (1, ctx.n_tokens, hidden), torch.float32)
         api.weighted_pair(mixed.tensor, 1.0, fed.tensor, 1.0, both)
         return Delta(both)
+
+
+@ARRANGEMENTS.register("sandwich")
+class Sandwich(Arrangement):
+    """``h += post(mixer(pre(h))); h += post'(ffn(pre'(h)))`` with four norms (the feed-forward and its two may be left
+    out).  With a ``depth`` part the stream at the layer's end is kept as result ``result_index`` of ``results`` (the
+    embedding's output is result 0, kept by the first layer before its first norm) and replaced by the weighted sum of
+    results ``0 .. result_index``.  A sublayer's output is normalised before the stream takes it, so no part may add
+    into the stream itself."""
+
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "mixer_post_norm": "norm", "ffn_norm": "norm", "ffn": "ffn", "ffn_post_norm": "norm",
+             "depth": "depth"}
+    optional = ("ffn_norm", "ffn", "ffn_post_norm", "depth")
+
+    def __init__(self, parts, result_index: int = 0, results: int = 0):
+        super().__init__(parts)
+        present = [role in parts for role in ("ffn_norm", "ffn", "ffn_post_norm")]
+        if any(present) and not all(present):
+            raise ValueError("a sandwich layer has a feed-forward and both of its norms, or none of the three")
+        self.result_index, self.results = int(result_index), int(results)
+        if "depth" in parts and not 1 <= self.result_index < self.results:
+            raise ValueError(f"a layer that mixes results needs its place among them, got {result_index} of {results}")
+
+    def mixers(self):
+        return [self.parts["mixer"]]
+
+    def device_driven(self) -> bool:
+        return all(part.device_driven() for part in self.parts.values())
+
+    def run(self, ctx, residual, pending: Delta | None, caches, states) -> Delta:
+        hidden = residual.shape[-1]
+        ctx.residual = None                     # outputs pass a norm before the stream takes them
+        depth = self.parts.get("depth")
+        kept = None
+        if depth is not None:
+            kept = ctx.scratch("model.results", (self.results, ctx.n_tokens, hidden), torch.float32)
+            if pending is None:                 # the first layer: the embedding's output is result 0
+                pending = Delta(None, depth=DepthStep(kept, 0, None))
+        normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
+        self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
+        last = self.parts["mixer"].forward(ctx, normed, caches[0], states[0])
+        last = Delta(last.tensor, post=self.parts["mixer_post_norm"].after())
+        if "ffn" in self.parts:
+            self.parts["ffn_norm"].forward(ctx, residual, last, normed)
+            last = self.parts["ffn"].forward(ctx, normed)
+            last = Delta(last.tensor, post=self.parts["ffn_post_norm"].after())
+        if depth is not None:
+            last.depth = DepthStep(kept, self.result_index, depth.weight)
+        return last

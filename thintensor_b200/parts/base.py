@@ -22,6 +22,8 @@ Roles and what each must provide:
   (the previous token, say).  ``Head``: ``forward(ctx, x) -> logits``.
 * ``InputShift``: ``forward(ctx, x, states) -> tensor``: what a mixer reads instead of the normed rows themselves
   (a blend with the previous token's rows, kept as a per-sequence state).
+* ``DepthMix``: the weights with which a layer's end mixes the results of the layers so far (``weights()`` only; the
+  arrangement hands them to the norm that follows).
 * ``Arrangement``: wires norms, mixer and feed-forward around the residual stream.
 """
 from __future__ import annotations
@@ -35,7 +37,8 @@ import torch
 @dataclass(frozen=True)
 class WeightDecl:
     """A tensor a part needs.  ``init`` tells the random-weights mode how to draw it:
-    ``normal`` is N(0, 0.02), ``norm`` is 1 + N(0, 0.1), ``zeros`` is zero.
+    ``normal`` is N(0, 0.02), ``norm`` is 1 + N(0, 0.1), ``small`` is N(0, 0.1), ``depth`` is N(0, 0.3) with one added to the last number,
+    ``zeros`` is zero.
     ``alias_of`` names a checkpoint tensor (full name) to use instead when this one is
     absent from the checkpoint; with ``prefer_alias`` it is used even when this one is
     stored (a tied output head, whose stored copy is ignored)."""
@@ -58,6 +61,7 @@ class KVNeed:
     head_dim: int
     window: int | None = None
     value_dim: int | None = None        # numbers per value head where they differ from the keys' (None: head_dim)
+    every: int = 1                      # one entry for each ``every`` tokens: entry n belongs to tokens n * every .. n * every + every - 1
 
     @property
     def v_dim(self) -> int:
@@ -73,14 +77,40 @@ class StateNeed:
     dtype: torch.dtype = torch.float32
 
 
+@dataclass(frozen=True)
+class PostNorm:
+    """An RMS norm applied to a sublayer's output before the stream takes it: ``v / sqrt(mean(v^2) + eps) * (weight + offset)``."""
+
+    weight: torch.Tensor        # float32 [hidden]
+    eps: float
+    offset: float = 0.0
+
+
+@dataclass(frozen=True)
+class DepthStep:
+    """The stream after the addition is result ``index`` of ``results`` (float32 ``[count, tokens, hidden]``; result 0 is the
+    embedding's output); what goes on is ``sum(weights[j] * results[j] for j <= index)``.  Without ``weights`` the
+    stream is only kept (the embedding's output, before the first layer)."""
+
+    results: torch.Tensor
+    index: int
+    weights: torch.Tensor | None    # float32 [index + 1]
+
+
 @dataclass
 class Delta:
     """What a mixer or feed-forward adds to the residual stream: float32
     ``[splits, tokens, hidden]``; the sum over ``splits`` is the value.  The norm that
     follows does the sum and the addition.  ``tensor`` is None when the part has already
-    added its result into the stream itself (``ctx.residual``, where the arrangement offers it)."""
+    added its result into the stream itself (``ctx.residual``, where the arrangement offers it).
+
+    ``post``: the sum is normalised (RMS norm with this weight) before it is added.  ``depth``: after the
+    addition the stream is kept as a layer's result and replaced by a weighted sum of the results so far.
+    Both are carried out by the norm that follows, in its one pass over the row."""
 
     tensor: torch.Tensor | None
+    post: "PostNorm | None" = None
+    depth: "DepthStep | None" = None
 
     @property
     def splits(self) -> int:
@@ -150,6 +180,11 @@ class PositionEncoding(Part):
 
 class Mixer(Part):
     def cache_need(self) -> KVNeed | None:
+        return None
+
+    def summary_need(self) -> KVNeed | None:
+        """A second, coarser cache beside the mixer's keys and values: one key and one value for each ``every`` tokens
+        (the means of whole blocks of tokens, say).  ``forward`` finds it as ``cache.summary``."""
         return None
 
     def state_needs(self) -> list[StateNeed]:
@@ -252,6 +287,7 @@ NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")
 FEED_FORWARDS = Registry("feed-forward")
+DEPTH_MIXES = Registry("depth mix")
 EMBEDDINGS = Registry("embedding")
 SHIFTS = Registry("input shift")
 HEADS = Registry("head")
@@ -262,6 +298,7 @@ REGISTRIES = {
     "position": POSITION_ENCODINGS,
     "mixer": MIXERS,
     "ffn": FEED_FORWARDS,
+    "depth": DEPTH_MIXES,
     "embedding": EMBEDDINGS,
     "shift": SHIFTS,
     "head": HEADS,

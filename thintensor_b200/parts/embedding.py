@@ -3,7 +3,8 @@
 ``h0 = E[token] * scale`` with scale 1 for Llama (thinruntime/gpu_runtime.py:10072,
 thinruntime/model_arch.py:234-238).  The head is ``lm_head.weight`` when the checkpoint
 has one and the embedding table otherwise (thinruntime/gpu_runtime.py:10395-10401);
-logits are float32.
+logits are float32.  Two more embeddings add a second row to the token's: one chosen by the pair of the
+previous token and this one, one by the token's position.
 """
 from __future__ import annotations
 
@@ -32,6 +33,30 @@ class TokenEmbedding(Embedding):
 
     def forward(self, ctx, tokens, residual, states=None) -> None:
         api.embed_gather(self.table, tokens, residual, self.scale, ctx.status)
+
+
+@EMBEDDINGS.register("table_positions")
+class PositionedEmbedding(TokenEmbedding):
+    """The token's row plus a learned vector of the token's position: ``h0 = E[token] * scale + P[position]`` with
+    ``positions`` rows in ``P``; positions count from 0 in each sequence.  A token at a position beyond the table raises
+    the status word's bad-token bit (its row is zero); the engine refuses such a step beforehand (``max_positions``)."""
+
+    def __init__(self, vocab: int, hidden: int, positions: int, scale: float = 1.0, name: str = "weight", position_name: str = "positions.weight"):
+        super().__init__(vocab, hidden, scale, name)
+        self.max_positions = int(positions)
+        self.position_name = position_name
+        self.position_table: torch.Tensor | None = None
+
+    def weights(self) -> dict[str, WeightDecl]:
+        return {**super().weights(), self.position_name: WeightDecl((self.max_positions, self.hidden))}
+
+    def bind(self, tensors, dtype, device) -> None:
+        super().bind(tensors, dtype, device)
+        self.position_table = tensors[self.position_name].to(self.table.dtype).contiguous()
+
+    def forward(self, ctx, tokens, residual, states=None) -> None:
+        api.embed_position_gather(self.table, self.position_table, tokens, ctx.cu, ctx.len_before, ctx.sequences, residual, self.scale,
+                                  ctx.status)
 
 
 @EMBEDDINGS.register("table_pair_hash")

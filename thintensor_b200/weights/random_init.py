@@ -3,7 +3,8 @@
 The reference has no such mode; its tiny fixtures are freshly initialised library
 models saved as bfloat16 safetensors (benchmark_results/operator_graph_matrix.md:5-10).
 Here every declared tensor is drawn on the CPU from one generator seeded with ``seed``,
-in declaration order: matrices and tables N(0, 0.02), norm weights 1 + N(0, 0.1).
+in declaration order: matrices and tables N(0, 0.02), norm weights 1 + N(0, 0.1) (N(0, 0.1) where they are stored
+as the distance from one).
 """
 from __future__ import annotations
 
@@ -28,6 +29,12 @@ def draw(decl: WeightDecl, generator: torch.Generator) -> torch.Tensor:
         return 1.0 + 0.1 * noise
     if decl.init == "normal":
         return 0.02 * noise
+    if decl.init == "small":
+        return 0.1 * noise
+    if decl.init == "depth":                # weights of a sum over earlier results: the newest counts most, none vanishes
+        weights = 0.3 * noise
+        weights.view(-1)[-1] += 1.0
+        return weights
     raise ValueError(f"unknown initialisation {decl.init!r}")
 
 

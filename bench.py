@@ -110,6 +110,7 @@ def reference_arm(config: dict, steps: int, warmup: int) -> int:
 
 FAMALORN_SHAPES = {"1b": "famalorn-w2048", "3b": "famalorn-w3072"}
 NERUZEN_SHAPES = {"1b": "neruzen-w2048", "3b": "neruzen-w3072"}
+SOGIDRA_SHAPES = {"1b": "sogidra-w2048", "3b": "sogidra-w3072"}
 
 
 def neruzen_pair(size: str) -> tuple[dict, dict]:
@@ -119,6 +120,17 @@ def neruzen_pair(size: str) -> tuple[dict, dict]:
     attention.  Every Neruzen layer has the mixture of experts: 16 experts of 1,024 of which a token takes 4, and a shared
     expert of 4,096, so a token's feed-forward is as wide as Famalorn's dense one (8,192)."""
     return json.loads(json.dumps(SHAPES[NERUZEN_SHAPES[size]])), json.loads(json.dumps(SHAPES[FAMALORN_SHAPES[size]]))
+
+
+def sogidra_pair(size: str) -> tuple[dict, dict]:
+    """(Sogidra config.json, Llama config.json) of one size from the table of named shapes: the same width, feed-forward
+    width, vocabulary and number of layers (six).  The Llama decoder is the closest model: both are attention over the
+    block cache with a dense feed-forward.  Sogidra's differential layers have half as many heads with two maps of 64
+    numbers and values of 128, its window layers heads of 128 with a window of 1,024 tokens and blocks of 64."""
+    sogidra = json.loads(json.dumps(SHAPES[SOGIDRA_SHAPES[size]]))
+    llama = dict(SHAPES[SHAPE_NAMES[size]])
+    llama["num_hidden_layers"] = len(sogidra["layers"])
+    return sogidra, llama
 
 
 def famalorn_pair(size: str) -> tuple[dict, dict]:
@@ -134,13 +146,14 @@ def famalorn_pair(size: str) -> tuple[dict, dict]:
 def design_bench(args) -> int:
     """``--design famalorn``: prefill and decode of the Famalorn design beside the Llama decoder at equal size (random
     weights, bfloat16), with each step's time by class of kernel against that class's bound.  ``--design neruzen``: the
-    same for the Neruzen design beside Famalorn.  One JSON line."""
+    same for the Neruzen design beside Famalorn, ``--design sogidra`` for the Sogidra design beside Llama.  One JSON line."""
     import thintensor_b200
     from thintensor_b200.benchmark import class_fractions, measure_classes, measure_decode, measure_prefill
 
     pk = peaks()
     import torch
-    names, pair = (("famalorn", "llama"), famalorn_pair) if args.design == "famalorn" else (("neruzen", "famalorn"), neruzen_pair)
+    names, pair = {"famalorn": (("famalorn", "llama"), famalorn_pair), "neruzen": (("neruzen", "famalorn"), neruzen_pair),
+                   "sogidra": (("sogidra", "llama"), sogidra_pair)}[args.design]
     out = {"bench": f"{names[0].capitalize()} beside {names[1].capitalize()} at equal width, feed-forward, vocabulary and layers; random weights, bfloat16",
            "prompt_len": args.prompt_len, "batch": args.batch, "peaks": pk, "sizes": {}}
     for size in args.sizes.split(","):
@@ -189,8 +202,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     parser.add_argument("--shape", choices=sorted(SHAPE_NAMES), default="1b", help="with --only: layer sizes of another model of the family")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
-    parser.add_argument("--design", choices=["famalorn", "neruzen"],
-                        help="measure this design beside the closest model the library has at equal size (Famalorn beside Llama, Neruzen beside Famalorn) instead of the headline")
+    parser.add_argument("--design", choices=["famalorn", "neruzen", "sogidra"],
+                        help="measure this design beside the closest model the library has at equal size (Famalorn beside Llama, Neruzen beside Famalorn, Sogidra beside Llama) instead of the headline")
     parser.add_argument("--sizes", default="1b,3b", help="with --design: which sizes (1b: width 2,048; 3b: width 3,072)")
     args = parser.parse_args()
     if args.design:

@@ -19,7 +19,7 @@ from .sampling.sampler import SamplingParams
 
 # Named shapes for benchmarks with random weights, each a whole config.json: the three Llama 3
 # models the reference's reports measure, two tiny ones that differ in every size and option, and
-# two Famalorn and two Neruzen models of six layers at the widths of the 1B and 3B Llama shapes.
+# two Famalorn, two Neruzen and two Sogidra models of six layers at the widths of the 1B and 3B Llama shapes.
 # They are data (config/shapes.json), read here and by bench.py.
 SHAPES: dict[str, dict] = json.loads((Path(__file__).resolve().parent / "config" / "shapes.json").read_text(encoding="utf-8"))
 
@@ -84,11 +84,14 @@ def kv_read_bytes_per_token(model) -> int:
 
 def kv_read_bytes(model, context: float) -> float:
     """Bytes of keys and values a decode step reads for one sequence of ``context`` cached tokens: a run with a window
-    reads only the window's tokens."""
+    reads only the window's tokens, a coarser cache (a mixer's summary) one entry for each of its blocks."""
     kv, _, _ = model.cache_needs()
     width = torch.empty((), dtype=model.dtype).element_size()
-    return sum(need.kv_heads * (need.head_dim + need.v_dim) * width * (context if need.window is None else min(context, need.window))
-               for need in kv if need is not None)
+    def entries(need) -> float:     # a coarser cache holds one entry for each ``every`` tokens; a run with a window reads the window
+        held = context / need.every
+        return held if need.window is None else min(held, need.window)
+
+    return sum(need.kv_heads * (need.head_dim + need.v_dim) * width * entries(need) for need in kv if need is not None)
 
 
 def state_bytes_per_sequence(model) -> int:
@@ -126,7 +129,9 @@ def attention_flops(model, tokens: int) -> float:
             if kv[user] is not None:
                 window = kv[user].window
                 pairs = tokens * (tokens + 1) / 2
-                if window is not None and window < tokens:
+                if hasattr(mixer, "visible_pairs"):         # a mask of the mixer's own (a window with pooled blocks before it)
+                    pairs = mixer.visible_pairs(tokens)
+                elif window is not None and window < tokens:
                     pairs = window * (window + 1) / 2 + (tokens - window) * window
                 dims = sum(getattr(mixer, "pair_dims", (kv[user].head_dim, kv[user].v_dim)))
                 flops += 2.0 * pairs * dims * getattr(mixer, "heads", kv[user].kv_heads)
@@ -188,12 +193,13 @@ def class_fractions(model, classes: dict, pk: dict, prefill_prompts: list[list[i
     and its attention against it too (the cache it reads); the rest (norms, rotation, embedding,
     sampling) has no bound worth naming and is given as time alone.  Times are those of kernels run
     one after another (see :func:`measure_classes`)."""
+    attention_kernels = ("tt_attention", "tt_latent_attention", "tt_differential_attention", "tt_pooled_window_attention")
     recurrent = ("tt_mamba2_scan", "tt_delta_scan", "tt_causal_conv", "tt_gated_group_norm", "tt_decay_scan", "tt_linear_attention_prepare")
 
     def split(spans: dict) -> dict:
         out = {"products": 0.0, "attention": 0.0, "recurrence": 0.0, "rest": 0.0}
         for name, entry in spans.items():
-            kind = ("products" if name.startswith("tt_gemm") else "attention" if name.startswith(("tt_attention", "tt_latent_attention"))
+            kind = ("products" if name.startswith("tt_gemm") else "attention" if name.startswith(attention_kernels)
                     else "recurrence" if name.startswith(recurrent) else "rest")
             out[kind] += entry["ms"]
         return out

@@ -8,9 +8,27 @@ captured in a CUDA graph can be replayed while a kernel advances the lengths.
 """
 from __future__ import annotations
 
+import contextlib
+import gc
 from dataclasses import dataclass, field
 
 import torch
+
+
+@contextlib.contextmanager
+def capture(graph: "torch.cuda.CUDAGraph"):
+    """``torch.cuda.graph(graph)`` with Python's cyclic collector held off until the capture has ended.  A collection in
+    the middle of a capture may free an older engine's graphs, and destroying a graph is not permitted while any stream
+    of the process captures: the capture would end invalid."""
+    was_on = gc.isenabled()
+    gc.collect()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            yield
+    finally:
+        if was_on:
+            gc.enable()
 
 
 class Workspace:

@@ -22,7 +22,7 @@ import torch
 
 from ..cache.cache import SequenceCache
 from ..kernels import api
-from .context import StepContext, Workspace
+from .context import StepContext, Workspace, capture
 from .model import DecoderModel
 
 
@@ -199,7 +199,7 @@ class Engine:
         if entry.graph is None or entry.generation != self.workspace.generation:
             entry.generation = self.workspace.generation
             entry.graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(entry.graph):                             # captures; the step runs at the replay below
+            with capture(entry.graph):                                      # captures; the step runs at the replay below
                 entry.logits = self.model.forward(ctx, self.cache, rows)
             if self.workspace.generation != entry.generation:
                 self.step_graphs.pop(key)

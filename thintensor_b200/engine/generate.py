@@ -24,7 +24,7 @@ import torch
 
 from ..kernels import api
 from ..sampling.sampler import SamplingParams, sample
-from .context import StepContext
+from .context import StepContext, capture
 from .engine import Engine, Entry
 
 
@@ -301,7 +301,7 @@ class _DecodeState:
                 generation = e.workspace.generation
                 graph = torch.cuda.CUDAGraph()
                 # capture replays nothing; the captured step runs at the first replay
-                with torch.cuda.graph(graph):
+                with capture(graph):
                     body(params)
                 if e.workspace.generation != generation:
                     raise RuntimeError("scratch memory moved while a decode step was being captured")

@@ -71,6 +71,11 @@ class DifferentialAttention(Mixer):
     def cache_need(self) -> KVNeed:
         return KVNeed(self.kv_heads, 2 * self.dim, None, None if self.value_dim == 2 * self.dim else self.value_dim)
 
+    @property
+    def pair_dims(self) -> tuple[int, int]:
+        """What a (query, key) pair costs: two scores of ``dim`` numbers and the value taken twice, once per map."""
+        return 2 * self.dim, 2 * self.value_dim
+
     def bind(self, tensors, dtype, device) -> None:
         n = self.names
         keys = ("q", "k", "v") if self.own_keys else ("q",)
@@ -140,6 +145,10 @@ class PooledWindowAttention(Mixer):
 
     def summary_need(self) -> KVNeed:
         return KVNeed(self.kv_heads, self.dim, None, None, self.pool)
+
+    def visible_pairs(self, tokens: int) -> float:
+        """(query, key) pairs of one sequence of ``tokens`` tokens: the window's tokens and the whole blocks before it."""
+        return float(sum(min(i + 1, self.window) + max(0, i - self.window + 1) // self.pool for i in range(tokens)))
 
     def bind(self, tensors, dtype, device) -> None:
         n = self.names

@@ -288,9 +288,9 @@ def test_logits_do_not_depend_on_the_batch(folders, name):
     from thintensor_b200.engine.engine import Entry
 
     folder = folders(name, "float32")
-    engine = load(folder, "float32").new_engine(max_tokens=1024, max_sequences=4, step_graphs=False)
+    engine = load(folder, "float32").new_engine(max_tokens=1024, max_sequences=5, step_graphs=False)
     vocab = CONFIGS[name]["vocab"]
-    prompts = [token_ids(vocab, n, 500 + n) for n in (33, 70, 5)]
+    prompts = [token_ids(vocab, n, 500 + n) for n in (33, 70, 17, 5)]
     alone = []
     for p in prompts:
         slot = engine.open()
@@ -303,7 +303,10 @@ def test_logits_do_not_depend_on_the_batch(folders, name):
     # plain implementation's own rounding to float32 at that position
     carried = torch.stack([oracle_float32_drift(folder, p)[-1] for p in prompts]).to(alone.device)
     err = (together - alone).abs().max(dim=-1).values
-    assert bool((err <= 2e-6 * float(alone.abs().max()) + 4.0 * carried).all()), (err, carried)
+    # up to 16 tokens alone go through the exact product's form for few rows, which sums k in another order than the
+    # tiled form that the batch uses; longer requests use the tiled form both times
+    few = torch.tensor([16.0 if len(p) <= 16 else 4.0 for p in prompts], device=alone.device)
+    assert bool((err <= 2e-6 * float(alone.abs().max()) + few * carried).all()), (err, carried)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -323,6 +323,435 @@ __global__ void pooled_window_rows_kernel(const T* __restrict__ q, const T* __re
     }
 }
 
+
+// ------------------------------------------------------------------------------------------------ tensor cores
+// Both forms for bfloat16 on tensor cores (mma.sync m16n8k16, float32 accumulators and softmax), prompts and decoding.
+//
+// A CTA owns 64 query rows of one sequence and one key/value head, four tiles of 16 rows ((token, head of the group)
+// pairs), and a slice of the blocks of 64 keys that those rows see.  Every block's K and V tiles are copied once per CTA
+// into shared memory with cp.async, one or two blocks ahead.  With two maps a second set of four warps owns the same rows
+// for map 2: it reads the other half of the query and key rows and the same value tile, so that a warp's arithmetic is that
+// of an ordinary head with KD score dimensions and VD value dimensions, and the two sets meet in shared memory at the end
+// (o = a1 - lambda a2, the division by the root mean square over the head, the gain).  With pooled blocks the list of
+// blocks starts with those of the coarser cache, whose entry n a row at position i sees if n < floor((i - window + 1) / every).
+//
+// The B operands are 16-byte (for a last half chunk of the score dimensions 8-byte) pieces of cache rows: the k index of
+// Q K^T is permuted alike in Q and K, the key index of P V alike in P's columns and V's rows (score column n of score
+// tile j stands for key fm_key_of(j, n)), and values lie transposed inside a cache block.
+// Slices of the keys (grid.z) leave (max, sum, accumulator) per row and map in the scratch of the exact kernels, in natural
+// logarithm units, for the same merge kernels.
+
+__device__ __forceinline__ void fm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t fm_pack(float lo, float hi) {
+    const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float fm_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+// cap * tanh(s / cap) through one exponential: tanh(x) = 1 - 2 / (e^(2x) + 1); absolute error about 1e-7 * cap.
+__device__ __forceinline__ float fm_cap(float s, float cap, float two_log2e_over_cap) {
+    const float e = fm_exp2(s * two_log2e_over_cap);
+    return cap - __fdividef(2.0f * cap, e + 1.0f);
+}
+__device__ __forceinline__ int fm_key_of(int j, int n) { return 32 * (j >> 2) + 8 * (n >> 1) + 2 * (j & 3) + (n & 1); }
+__device__ __forceinline__ void fm_cp16(void* smem_dst, const void* src) {
+    const uint32_t dst = (uint32_t)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void fm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void fm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+constexpr int FM_TILES = 4;             // 16-row tiles of a CTA
+
+template <int KD, int VD, int MAPS> struct FormShape {
+    static_assert(KD % 16 == 0 && VD % 8 == 0, "score dimensions in halves of a 32-wide chunk, value dimensions in 8-wide tiles");
+    static constexpr int KC = KD / 32;                          // whole 32-wide chunks of a map's score dimensions
+    static constexpr bool HALF = (KD % 32) != 0;                // and a last chunk of 16
+    static constexpr int NT = VD / 8;
+    static constexpr int K_ROW = MAPS * KD * 2;                 // bytes of one cached key row
+    static constexpr bool K_SWIZZLE = (K_ROW % 128) == 0;       // rows that would start on the same bank
+    static constexpr int K_TILE = 64 * K_ROW;
+    static constexpr int V_TILE = VD * 128;
+    static constexpr int STAGE = K_TILE + V_TILE;
+    static constexpr int STAGES = STAGE <= 16384 ? 3 : 2;
+    static constexpr int THREADS = FM_TILES * MAPS * 32;
+    static constexpr int EXCHANGE = MAPS == 2 ? FM_TILES * 16 * VD * 4 : 0;    // map 2's output on its way to map 1's warps
+    static constexpr int SHARED = STAGES * STAGE > EXCHANGE ? STAGES * STAGE : EXCHANGE;
+};
+
+template <int KD, int VD> struct FormState {
+    static constexpr int KC = KD / 32, NT = VD / 8;
+    uint32_t qa[KC + 1][4], qb[KC + 1][4];      // Q fragments of rows g and g + 8, score dimensions permuted
+    float o[NT][4];
+    float m_run[2], l_run[2];
+};
+
+// One block of 64 keys or entries: S = Q K^T, scale, cap, mask (row i sees index n if lo[i] <= n <= hi[i]), running softmax
+// in base 2, O += P V.  load_k(j, c) returns the 16 bytes of key fm_key_of(j, g) at dimensions 32c + 8t .. + 7, load_k_half(j)
+// its 8 bytes at 32 KC + 4t .. + 3; load_v(n, half) the 16 bytes of value dimension 8n + g at keys 32 half + 8t .. + 7.
+template <int KD, int VD, typename LoadK, typename LoadKHalf, typename LoadV>
+__device__ __forceinline__ void form_block_math(FormState<KD, VD>& st, int index_base, const int (&lo)[2], const int (&hi)[2], int t,
+                                                float scale, float cap, LoadK load_k, LoadKHalf load_k_half, LoadV load_v) {
+    constexpr int KC = KD / 32, NT = VD / 8;
+    constexpr bool HALF = (KD % 32) != 0;
+    constexpr float LOG2E = 1.4426950408889634f;
+    float s[8][4];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+#pragma unroll
+        for (int c = 0; c < KC; ++c) {
+            const uint4 kr = load_k(j, c);
+            fm_mma(s[j], st.qa[c][0], st.qb[c][0], st.qa[c][1], st.qb[c][1], kr.x, kr.y);
+            fm_mma(s[j], st.qa[c][2], st.qb[c][2], st.qa[c][3], st.qb[c][3], kr.z, kr.w);
+        }
+        if constexpr (HALF) {
+            const uint2 kr = load_k_half(j);
+            fm_mma(s[j], st.qa[KC][0], st.qb[KC][0], st.qa[KC][1], st.qb[KC][1], kr.x, kr.y);
+        }
+    }
+    const bool all_visible = index_base >= max(lo[0], lo[1]) && index_base + TT_BLOCK_TOKENS - 1 <= min(hi[0], hi[1]);
+    const float to_log2 = cap > 0.0f ? LOG2E : scale * LOG2E;
+    const float cap_factor = cap > 0.0f ? 2.0f * LOG2E / cap : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                float v = s[j][2 * i + e];
+                if (cap > 0.0f) v = fm_cap(v * scale, cap, cap_factor);
+                v *= to_log2;
+                if (!all_visible) {
+                    const int index = index_base + fm_key_of(j, 2 * t + e);
+                    if (index < lo[i] || index > hi[i]) v = -INFINITY;
+                }
+                s[j][2 * i + e] = v;
+                mx = fmaxf(mx, v);
+            }
+        }
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+        mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+        const float m_new = fmaxf(st.m_run[i], mx);
+        const float corr = (m_new == -INFINITY) ? 1.0f : fm_exp2(st.m_run[i] - m_new);
+        const float base = (m_new == -INFINITY) ? 0.0f : m_new;
+        float sum = 0.0f;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float p = fm_exp2(s[j][2 * i + e] - base);
+                s[j][2 * i + e] = p;
+                sum += p;
+            }
+        }
+        st.l_run[i] = st.l_run[i] * corr + sum;
+        st.m_run[i] = m_new;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { st.o[n][2 * i] *= corr; st.o[n][2 * i + 1] *= corr; }
+    }
+    uint32_t pa[4][4];
+#pragma unroll
+    for (int mm = 0; mm < 4; ++mm) {
+        pa[mm][0] = fm_pack(s[2 * mm][0], s[2 * mm][1]);
+        pa[mm][1] = fm_pack(s[2 * mm][2], s[2 * mm][3]);
+        pa[mm][2] = fm_pack(s[2 * mm + 1][0], s[2 * mm + 1][1]);
+        pa[mm][3] = fm_pack(s[2 * mm + 1][2], s[2 * mm + 1][3]);
+    }
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const uint4 vr = load_v(n, half);
+            fm_mma(st.o[n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr.x, vr.y);
+            fm_mma(st.o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
+        }
+    }
+}
+
+struct FormArgs {
+    const __nv_bfloat16 *q, *k_pool, *v_pool;
+    const int* table;
+    int table_width, pool_blocks;
+    const __nv_bfloat16 *mean_k, *mean_v;       // the coarser cache (pooled blocks only)
+    const int* mean_table;
+    int mean_width, mean_blocks, every;
+    const int *cu, *len_before;
+    int sequences, heads, kv_heads, tokens_per_tile, cta_tiles, window, splits;
+    float scale, cap, lambda, gain, eps;
+    __nv_bfloat16* out;
+    float *part_acc, *part_ml;
+    unsigned* status;
+};
+
+template <int KD, int VD, int MAPS, bool POOLED>
+__global__ void __launch_bounds__(FormShape<KD, VD, MAPS>::THREADS)
+form_kernel(const FormArgs a) {
+    using S = FormShape<KD, VD, MAPS>;
+    constexpr int KC = S::KC, NT = S::NT, STAGES = S::STAGES, ROW = MAPS * KD;
+    extern __shared__ uint4 form_stage_mem[];                  // [STAGES][K tile, V tile]; at the end map 2's output
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
+    const int my_tile = warp & (FM_TILES - 1), map = warp / FM_TILES;
+    const int kh = blockIdx.x;
+    const int group = a.heads / a.kv_heads;
+    const int tokens_per_cta = a.tokens_per_tile * FM_TILES;
+
+    // which sequence and which of its CTA tiles; late tiles of a sequence come first
+    int tile = a.cta_tiles - 1 - (int)blockIdx.y;
+    int b = -1;
+    for (int base = 0; base < a.sequences && b < 0; base += 32) {
+        const int mine = base + lane;
+        const int count = mine < a.sequences ? (a.cu[mine + 1] - a.cu[mine] + tokens_per_cta - 1) / tokens_per_cta : 0;
+        int prefix = count;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, prefix, o);
+            if (lane >= o) prefix += up;
+        }
+        const unsigned owner = __ballot_sync(0xffffffffu, tile < prefix);
+        if (owner) {
+            const int first = __ffs(owner) - 1;
+            b = base + first;
+            tile -= __shfl_sync(0xffffffffu, prefix - count, first);
+        } else {
+            tile -= __shfl_sync(0xffffffffu, prefix, 31);
+        }
+    }
+    if (b < 0) return;                 // a spare CTA (the grid is an upper bound): all its warps leave together
+    const int seq_begin = a.cu[b], seq_new = a.cu[b + 1] - seq_begin, before = a.len_before[b];
+    const int cta_tok0 = tile * tokens_per_cta;
+    const int cta_tokens = min(tokens_per_cta, seq_new - cta_tok0);
+    const int tok0 = cta_tok0 + my_tile * a.tokens_per_tile;
+    const int tile_tokens = max(0, min(a.tokens_per_tile, seq_new - tok0));      // 0: the warp only helps copying
+
+    // what a position sees: tokens first_of(p) .. p, and the entries 0 .. lead_of(p) - 1 of the coarser cache
+    auto first_of = [&](int p) { return (POOLED && p - a.window + 1 > 0) ? p - a.window + 1 : 0; };
+    auto lead_of = [&](int p) { return (POOLED && p - a.window + 1 > 0) ? (p - a.window + 1) / a.every : 0; };
+
+    FormState<KD, VD> st;
+    size_t row_at[2];                  // token * heads + head
+    bool row_ok[2];
+    int tok_lo[2], tok_hi[2], lead_hi[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const int r = g + 8 * i;
+        const int local = r / group;
+        row_ok[i] = local < tile_tokens;
+        row_at[i] = (size_t)(seq_begin + tok0 + local) * a.heads + kh * group + (r - local * group);
+        const int pos = row_ok[i] ? before + tok0 + local : -1;
+        tok_hi[i] = pos;
+        tok_lo[i] = first_of(pos);
+        lead_hi[i] = lead_of(pos) - 1;
+    }
+    {
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int c = 0; c < KC; ++c) {
+            const uint4 va = row_ok[0] ? *reinterpret_cast<const uint4*>(a.q + row_at[0] * ROW + map * KD + 32 * c + 8 * t) : zero4;
+            const uint4 vb = row_ok[1] ? *reinterpret_cast<const uint4*>(a.q + row_at[1] * ROW + map * KD + 32 * c + 8 * t) : zero4;
+            st.qa[c][0] = va.x; st.qa[c][1] = va.y; st.qa[c][2] = va.z; st.qa[c][3] = va.w;
+            st.qb[c][0] = vb.x; st.qb[c][1] = vb.y; st.qb[c][2] = vb.z; st.qb[c][3] = vb.w;
+        }
+        if constexpr (S::HALF) {
+            const uint2 zero2 = make_uint2(0, 0);
+            const uint2 va = row_ok[0] ? *reinterpret_cast<const uint2*>(a.q + row_at[0] * ROW + map * KD + 32 * KC + 4 * t) : zero2;
+            const uint2 vb = row_ok[1] ? *reinterpret_cast<const uint2*>(a.q + row_at[1] * ROW + map * KD + 32 * KC + 4 * t) : zero2;
+            st.qa[KC][0] = va.x; st.qa[KC][1] = va.y; st.qa[KC][2] = st.qa[KC][3] = 0;
+            st.qb[KC][0] = vb.x; st.qb[KC][1] = vb.y; st.qb[KC][2] = st.qb[KC][3] = 0;
+        }
+#pragma unroll
+        for (int n = 0; n < NT; ++n) { st.o[n][0] = st.o[n][1] = st.o[n][2] = st.o[n][3] = 0.0f; }
+        st.m_run[0] = st.m_run[1] = -INFINITY;
+        st.l_run[0] = st.l_run[1] = 0.0f;
+    }
+
+    // the CTA's list of blocks: those of the coarser cache that its last row sees, then the token blocks from the first one
+    // any of its rows sees to its last row's; this CTA takes slice blockIdx.z of the list
+    const int cta_lo = before + cta_tok0, cta_hi = before + cta_tok0 + cta_tokens - 1;
+    const int n_coarse = (lead_of(cta_hi) + TT_BLOCK_TOKENS - 1) / TT_BLOCK_TOKENS;
+    const int block0 = first_of(cta_lo) / TT_BLOCK_TOKENS, block1 = cta_hi / TT_BLOCK_TOKENS;
+    const int n_items = n_coarse + block1 - block0 + 1;
+    const int per = (n_items + a.splits - 1) / a.splits;
+    const int item0 = min(n_items, (int)blockIdx.z * per), item1 = min(n_items, item0 + per);
+    const int my_hi = tile_tokens > 0 ? before + tok0 + tile_tokens - 1 : -1;
+    const int my_first = first_of(before + tok0), my_lead = tile_tokens > 0 ? lead_of(my_hi) : 0;
+    const int* table_row = a.table + (size_t)b * a.table_width;
+    const int* mean_row = POOLED ? a.mean_table + (size_t)b * a.mean_width : nullptr;
+    uint8_t* stages = reinterpret_cast<uint8_t*>(form_stage_mem);
+    unsigned bad = 0;                                            // bit i % 32: item i has no usable data
+
+    auto issue = [&](int i) {                                    // all threads: copy item item0 + i into its stage
+        const int item = item0 + i;
+        if (item < item1) {
+            const bool coarse = POOLED && item < n_coarse;
+            const int block = coarse ? mean_row[item] : table_row[block0 + item - n_coarse];
+            if (block >= 0 && block < (coarse ? a.mean_blocks : a.pool_blocks)) {
+                const size_t at = (size_t)block * a.kv_heads + kh;
+                const uint8_t* ksrc = reinterpret_cast<const uint8_t*>((coarse ? a.mean_k : a.k_pool) + at * TT_BLOCK_TOKENS * ROW);
+                const uint8_t* vsrc = reinterpret_cast<const uint8_t*>((coarse ? a.mean_v : a.v_pool) + at * VD * TT_BLOCK_TOKENS);
+                uint8_t* kdst = stages + (size_t)(i % STAGES) * S::STAGE;
+                uint8_t* vdst = kdst + S::K_TILE;
+                constexpr int K_CHUNKS = S::K_ROW / 16;          // 16-byte chunks per key row
+                for (int c = threadIdx.x; c < S::K_TILE / 16; c += S::THREADS) {
+                    const int row = c / K_CHUNKS, ch = c - row * K_CHUNKS;
+                    const int to = S::K_SWIZZLE ? (ch ^ ((row & 1) << 2)) : ch;
+                    fm_cp16(kdst + row * S::K_ROW + to * 16, ksrc + (size_t)c * 16);
+                }
+                for (int c = threadIdx.x; c < S::V_TILE / 16; c += S::THREADS) {
+                    const int row = c >> 3, ch = c & 7;          // a value row is 64 tokens = 8 chunks
+                    fm_cp16(vdst + row * 128 + ((ch ^ ((row & 1) << 2)) * 16), vsrc + (size_t)c * 16);
+                }
+                bad &= ~(1u << (i & 31));
+            } else {
+                bad |= 1u << (i & 31);
+                if (threadIdx.x == 0) atomicOr(a.status, TT_STATUS_BAD_BLOCK);
+            }
+        }
+        fm_commit();
+    };
+
+#pragma unroll
+    for (int i = 0; i < STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < item1 - item0; ++i) {
+        fm_wait<STAGES - 2>();                // this thread's copies of item i are done ...
+        __syncthreads();                      // ... and so are everybody's; the stage of item i - 1 is free again
+        issue(i + STAGES - 1);
+        if ((bad >> (i & 31)) & 1u) continue;
+        const int item = item0 + i;
+        const bool coarse = POOLED && item < n_coarse;
+        const int index_base = (coarse ? item : block0 + item - n_coarse) * TT_BLOCK_TOKENS;
+        if (coarse) {
+            if (index_base >= my_lead) continue;                                                  // nothing for this warp here
+        } else if (index_base > my_hi || index_base + TT_BLOCK_TOKENS <= my_first) {
+            continue;
+        }
+        const uint8_t* ktile = stages + (size_t)(i % STAGES) * S::STAGE;
+        const uint8_t* vtile = ktile + S::K_TILE;
+        const int lo[2] = {coarse ? 0 : tok_lo[0], coarse ? 0 : tok_lo[1]};
+        const int hi[2] = {coarse ? lead_hi[0] : tok_hi[0], coarse ? lead_hi[1] : tok_hi[1]};
+        form_block_math<KD, VD>(st, index_base, lo, hi, t, a.scale, a.cap,
+                       [&](int j, int c) {
+                           const int row = fm_key_of(j, g), ch = map * (KD / 8) + 4 * c + t;
+                           const int at = S::K_SWIZZLE ? (ch ^ ((row & 1) << 2)) : ch;
+                           return *reinterpret_cast<const uint4*>(ktile + row * S::K_ROW + at * 16);
+                       },
+                       [&](int j) {
+                           const int row = fm_key_of(j, g), ch = map * (KD / 8) + 4 * KC + (t >> 1);
+                           const int at = S::K_SWIZZLE ? (ch ^ ((row & 1) << 2)) : ch;
+                           return *reinterpret_cast<const uint2*>(ktile + row * S::K_ROW + at * 16 + 8 * (t & 1));
+                       },
+                       [&](int n, int half) {
+                           const int row = 8 * n + g, ch = 4 * half + t;
+                           return *reinterpret_cast<const uint4*>(vtile + row * 128 + ((ch ^ ((row & 1) << 2)) * 16));
+                       });
+    }
+    fm_wait<0>();
+
+    // row sums live spread over the four threads of a quad
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 1);
+        st.l_run[i] += __shfl_xor_sync(0xffffffffu, st.l_run[i], 2);
+    }
+
+    if (a.splits > 1) {                 // this slice's (max, sum, accumulator) per row and map, for the merge kernel
+        constexpr float LN2 = 0.6931471805599453f;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            if (!row_ok[i]) continue;
+            const size_t slot = (row_at[i] * a.splits + blockIdx.z) * MAPS + map;
+            float* acc = a.part_acc + slot * VD + 2 * t;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) *reinterpret_cast<float2*>(acc + 8 * n) = make_float2(st.o[n][2 * i], st.o[n][2 * i + 1]);
+            if (t == 0) *reinterpret_cast<float2*>(a.part_ml + slot * 2) = make_float2(st.m_run[i] * LN2, st.l_run[i]);
+        }
+        return;
+    }
+
+    float inv[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) inv[i] = st.l_run[i] > 0.0f ? 1.0f / st.l_run[i] : 0.0f;
+    if constexpr (MAPS == 2) {
+        __syncthreads();                // every warp is through with the stages
+        float* exchange = reinterpret_cast<float*>(form_stage_mem) + (size_t)my_tile * 16 * VD;
+        if (map == 1) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i)
+#pragma unroll
+                for (int n = 0; n < NT; ++n)
+                    *reinterpret_cast<float2*>(exchange + (g + 8 * i) * VD + 8 * n + 2 * t) = make_float2(st.o[n][2 * i] * inv[i], st.o[n][2 * i + 1] * inv[i]);
+        }
+        __syncthreads();
+        if (map == 1) return;
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            float sumsq = 0.0f;
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                const float2 other = *reinterpret_cast<const float2*>(exchange + (g + 8 * i) * VD + 8 * n + 2 * t);
+                st.o[n][2 * i] = st.o[n][2 * i] * inv[i] - a.lambda * other.x;
+                st.o[n][2 * i + 1] = st.o[n][2 * i + 1] * inv[i] - a.lambda * other.y;
+                sumsq += st.o[n][2 * i] * st.o[n][2 * i] + st.o[n][2 * i + 1] * st.o[n][2 * i + 1];
+            }
+            sumsq += __shfl_xor_sync(0xffffffffu, sumsq, 1);
+            sumsq += __shfl_xor_sync(0xffffffffu, sumsq, 2);
+            inv[i] = rsqrtf(sumsq / (float)VD + a.eps) * a.gain;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        if (!row_ok[i]) continue;
+        __nv_bfloat16* dst = a.out + row_at[i] * VD + 2 * t;
+#pragma unroll
+        for (int n = 0; n < NT; ++n) *reinterpret_cast<uint32_t*>(dst + 8 * n) = fm_pack(st.o[n][2 * i] * inv[i], st.o[n][2 * i + 1] * inv[i]);
+    }
+}
+
+// Whether the tensor-core kernel takes these sizes; the launcher below instantiates exactly these.
+#define FM_DIFFERENTIAL_SHAPES(X) X(32, 64) X(48, 96) X(64, 128) X(64, 64) X(128, 128)
+#define FM_POOLED_SHAPES(X) X(32) X(64) X(96) X(128)
+
+template <int KD, int VD, int MAPS, bool POOLED>
+int form_launch(FormArgs a, int n_tokens, cudaStream_t stream) {
+    using S = FormShape<KD, VD, MAPS>;
+    auto kernel = form_kernel<KD, VD, MAPS, POOLED>;
+    static bool configured = false;
+    if (!configured) {
+        const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SHARED);
+        if (err != cudaSuccess) return (int)err;
+        configured = true;
+    }
+    a.tokens_per_tile = 16 / (a.heads / a.kv_heads);
+    const int tokens_per_cta = a.tokens_per_tile * FM_TILES;
+    a.cta_tiles = (n_tokens + tokens_per_cta - 1) / tokens_per_cta + a.sequences;       // upper bound; spare CTAs leave at once
+    if (a.cta_tiles > 65535 || a.kv_heads > 65535 || a.splits > 65535) return (int)cudaErrorInvalidValue;
+    return (int)tt_launch_pdl(kernel, dim3(a.kv_heads, a.cta_tiles, a.splits), dim3(S::THREADS), S::SHARED, stream, a);
+}
+
+// 0: done (or an error code); -1: sizes that the tensor-core kernel does not take
+int form_differential(const FormArgs& a, int dim, int value_dim, int n_tokens, cudaStream_t stream) {
+#define X(KD_, VD_) if (dim == KD_ && value_dim == VD_) return form_launch<KD_, VD_, 2, false>(a, n_tokens, stream);
+    FM_DIFFERENTIAL_SHAPES(X)
+#undef X
+    return -1;
+}
+int form_pooled(const FormArgs& a, int head_dim, int n_tokens, cudaStream_t stream) {
+#define X(HD_) if (head_dim == HD_) return form_launch<HD_, HD_, 1, true>(a, n_tokens, stream);
+    FM_POOLED_SHAPES(X)
+#undef X
+    return -1;
+}
 }  // namespace
 
 extern "C" int tt_differential_attention(const void* q, const void* k_pool, const void* v_pool, int dtype, const int* table,
@@ -337,6 +766,21 @@ extern "C" int tt_differential_attention(const void* q, const void* k_pool, cons
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
     const long long rows = (long long)n_tokens * heads;
     const dim3 grid((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS), (unsigned)splits);
+    if (dtype == TT_BF16 && heads / kv_heads <= 16) {          // tensor cores, for the sizes they are built for
+        FormArgs a = {};
+        a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+        a.table = table; a.table_width = table_width; a.pool_blocks = pool_blocks;
+        a.cu = cu; a.len_before = len_before; a.sequences = sequences; a.heads = heads; a.kv_heads = kv_heads; a.splits = splits;
+        a.scale = scale; a.lambda = lambda; a.gain = gain; a.eps = eps;
+        a.out = (__nv_bfloat16*)out; a.part_acc = part_acc; a.part_ml = part_ml; a.status = status;
+        const int code = form_differential(a, dim, value_dim, n_tokens, stream);
+        if (code > 0) return code;
+        if (code == 0) {
+            if (splits > 1)
+                tt_launch_pdl(differential_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, value_dim, rows, lambda, gain, eps, (__nv_bfloat16*)out);
+            TT_LAUNCH_CHECK();
+        }
+    }
     const size_t shared = (size_t)ATTN_WARPS * 2 * dim * sizeof(float);
     if (dtype == TT_F32) {
         tt_launch_pdl(differential_rows_kernel<float>, grid, dim3(ATTN_WARPS * 32), shared, stream, (const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, dim, value_dim, scale, lambda, gain, eps, splits, (float*)out, part_acc, part_ml, status);
@@ -377,6 +821,23 @@ extern "C" int tt_pooled_window_attention(const void* q, const void* k_pool, con
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
     const long long rows = (long long)n_tokens * heads;
     const dim3 grid((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS), (unsigned)splits);
+    if (dtype == TT_BF16 && heads / kv_heads <= 16) {          // tensor cores, for the sizes they are built for
+        FormArgs a = {};
+        a.q = (const __nv_bfloat16*)q; a.k_pool = (const __nv_bfloat16*)k_pool; a.v_pool = (const __nv_bfloat16*)v_pool;
+        a.table = table; a.table_width = table_width; a.pool_blocks = pool_blocks;
+        a.mean_k = (const __nv_bfloat16*)mean_k; a.mean_v = (const __nv_bfloat16*)mean_v; a.mean_table = mean_table;
+        a.mean_width = mean_width; a.mean_blocks = mean_blocks; a.every = every; a.window = window;
+        a.cu = cu; a.len_before = len_before; a.sequences = sequences; a.heads = heads; a.kv_heads = kv_heads; a.splits = splits;
+        a.scale = scale; a.cap = cap;
+        a.out = (__nv_bfloat16*)out; a.part_acc = part_acc; a.part_ml = part_ml; a.status = status;
+        const int code = form_pooled(a, head_dim, n_tokens, stream);
+        if (code > 0) return code;
+        if (code == 0) {
+            if (splits > 1)
+                tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (__nv_bfloat16*)out);
+            TT_LAUNCH_CHECK();
+        }
+    }
     const size_t shared = (size_t)ATTN_WARPS * head_dim * sizeof(float);
     if (dtype == TT_F32) {
         tt_launch_pdl(pooled_window_rows_kernel<float>, grid, dim3(ATTN_WARPS * 32), shared, stream, (const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, (const float*)mean_k, (const float*)mean_v, mean_table, mean_width, mean_blocks, every, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, scale, cap, window, splits, (float*)out, part_acc, part_ml, status);

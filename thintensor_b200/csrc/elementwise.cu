@@ -926,10 +926,31 @@ extern "C" int tt_activation(const float* x, int splits, long long split_stride,
 //   residual[r] = x                                                            (only when rows == nullptr)
 //   out[i] = x * rsqrt(mean(x^2) + eps) * (weight + weight_offset)
 // With `rows`, output row i comes from row rows[i] and neither the stream nor the results are written.
-// One block per output row; every thread keeps its numbers of the row in registers (PIECES float4 pieces when the
-// width is a multiple of four and at most 16384, else the row passes through shared memory).
+// One block per output row; the row passes through shared memory between the reductions, and a thread only ever
+// revisits its own numbers of it, four at a time when the width and the strides allow 16-byte accesses.
 // ------------------------------------------------------------------------------------
-template <typename TOut>
+// VEC numbers of a row at a time: 4 (16-byte loads and stores) when the width and every stride are multiples of four.
+template <int VEC> struct ChainPack { float v[VEC]; };
+template <int VEC> __device__ __forceinline__ ChainPack<VEC> chain_load(const float* p) {
+    ChainPack<VEC> r;
+    if constexpr (VEC == 4) {
+        const float4 x = *reinterpret_cast<const float4*>(p);
+        r.v[0] = x.x; r.v[1] = x.y; r.v[2] = x.z; r.v[3] = x.w;
+    } else {
+        r.v[0] = *p;
+    }
+    return r;
+}
+template <int VEC> __device__ __forceinline__ void chain_store(float* p, const ChainPack<VEC>& r) {
+    if constexpr (VEC == 4) *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+    else *p = r.v[0];
+}
+template <int VEC, typename TOut> __device__ __forceinline__ void chain_store_out(TOut* p, const ChainPack<VEC>& r) {
+    if constexpr (VEC == 4) tt_store4(p, r.v[0], r.v[1], r.v[2], r.v[3]);
+    else *p = tt_from_float<TOut>(r.v[0]);
+}
+
+template <typename TOut, int VEC>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_chain_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
                          const float* __restrict__ post_weight, float post_offset, float post_eps,
@@ -938,21 +959,28 @@ add_rmsnorm_chain_kernel(float* __restrict__ residual, const float* __restrict__
                          const int* __restrict__ rows, int hidden) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
-    extern __shared__ float chain_shared[];     // hidden floats (the row), then 32 for the reductions
+    extern __shared__ __align__(16) float chain_shared[];     // hidden floats (the row), then 32 for the reductions
     float* rowbuf = chain_shared;
     float* reduce = chain_shared + hidden;
     const int i = blockIdx.x;
     const int r = rows ? rows[i] : i;
     float* res = residual + (size_t)r * hidden;
+    const int first = threadIdx.x * VEC, step = blockDim.x * VEC;
+    using Pack = ChainPack<VEC>;
     // 1. the delta's slices, summed, and their mean square
     float sumsq = 0.0f;
     if (delta) {
         const float* del = delta + (size_t)r * hidden;
-        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-            float v = 0.0f;
-            for (int s = 0; s < splits; ++s) v += __ldg(del + (size_t)s * split_stride + j);
-            rowbuf[j] = v;
-            sumsq += v * v;
+        for (int j = first; j < hidden; j += step) {
+            Pack v = chain_load<VEC>(del + j);
+            for (int s = 1; s < splits; ++s) {
+                const Pack more = chain_load<VEC>(del + (size_t)s * split_stride + j);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) v.v[e] += more.v[e];
+            }
+            chain_store<VEC>(rowbuf + j, v);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) sumsq += v.v[e] * v.v[e];
         }
     } else {
         for (int j = threadIdx.x; j < hidden; j += blockDim.x) rowbuf[j] = 0.0f;
@@ -961,27 +989,48 @@ add_rmsnorm_chain_kernel(float* __restrict__ residual, const float* __restrict__
     if (post_weight) gain = rsqrtf(tt_block_sum(sumsq, reduce) / (float)hidden + post_eps);
     // 2. into the stream, kept as a result, mixed with the earlier results; every thread revisits its own numbers only
     sumsq = 0.0f;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-        float v = rowbuf[j];
-        if (post_weight) v = v * gain * (__ldg(post_weight + j) + post_offset);
-        float x = res[j] + v;
+    for (int j = first; j < hidden; j += step) {
+        Pack v = chain_load<VEC>(rowbuf + j);
+        if (post_weight) {
+            const Pack w = chain_load<VEC>(post_weight + j);
+#pragma unroll
+            for (int e = 0; e < VEC; ++e) v.v[e] = v.v[e] * gain * (w.v[e] + post_offset);
+        }
+        Pack x = chain_load<VEC>(res + j);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x.v[e] += v.v[e];
         if (results) {
             const float* mine = results + (size_t)r * hidden + j;
-            if (!rows) results[(size_t)index * result_stride + (size_t)r * hidden + j] = x;
+            if (!rows) chain_store<VEC>(results + (size_t)index * result_stride + (size_t)r * hidden + j, x);
             if (depth_weights) {
-                float mixed = 0.0f;
-                for (int k = 0; k < index; ++k) mixed = fmaf(__ldg(depth_weights + k), mine[(size_t)k * result_stride], mixed);
-                x = fmaf(__ldg(depth_weights + index), x, mixed);
+                Pack mixed;
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) mixed.v[e] = 0.0f;
+                for (int k = 0; k < index; ++k) {
+                    const float wk = __ldg(depth_weights + k);
+                    const Pack earlier = chain_load<VEC>(mine + (size_t)k * result_stride);
+#pragma unroll
+                    for (int e = 0; e < VEC; ++e) mixed.v[e] = fmaf(wk, earlier.v[e], mixed.v[e]);
+                }
+                const float wi = __ldg(depth_weights + index);
+#pragma unroll
+                for (int e = 0; e < VEC; ++e) x.v[e] = fmaf(wi, x.v[e], mixed.v[e]);
             }
         }
-        if (!rows) res[j] = x;
-        rowbuf[j] = x;
-        sumsq += x * x;
+        if (!rows) chain_store<VEC>(res + j, x);
+        chain_store<VEC>(rowbuf + j, x);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) sumsq += x.v[e] * x.v[e];
     }
     const float rstd = rsqrtf(tt_block_sum(sumsq, reduce) / (float)hidden + eps);
     TOut* o = out + (size_t)i * hidden;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x)
-        o[j] = tt_from_float<TOut>(rowbuf[j] * rstd * (__ldg(weight + j) + weight_offset));
+    for (int j = first; j < hidden; j += step) {
+        Pack x = chain_load<VEC>(rowbuf + j);
+        const Pack w = chain_load<VEC>(weight + j);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) x.v[e] = x.v[e] * rstd * (w.v[e] + weight_offset);
+        chain_store_out<VEC>(o + j, x);
+    }
 }
 
 extern "C" int tt_add_rmsnorm_chain(float* residual, const float* delta, int splits, long long split_stride, const float* post_weight,
@@ -990,15 +1039,22 @@ extern "C" int tt_add_rmsnorm_chain(float* residual, const float* delta, int spl
                                     int out_dtype, const int* rows, int n_rows, int hidden, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (hidden <= 0 || index < 0 || (depth_weights && !results)) return (int)cudaErrorInvalidValue;
-    int threads = hidden >= 4096 ? 1024 : hidden >= 1024 ? 512 : hidden >= 256 ? 256 : 128;
     const size_t shared = ((size_t)hidden + 32) * sizeof(float);
     if (shared > 200 * 1024) return (int)cudaErrorInvalidValue;
+    const bool wide = (hidden & 3) == 0 && (split_stride & 3) == 0 && (result_stride & 3) == 0 &&
+                      ((((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)post_weight | (uintptr_t)results | (uintptr_t)weight | (uintptr_t)out) & 15) == 0);
+    const int per_thread = wide ? 4 : 1;
+    int threads = hidden / per_thread >= 1024 ? 1024 : hidden / per_thread >= 512 ? 512 : hidden / per_thread >= 256 ? 256 : 128;
+#define TT_CHAIN_LAUNCH(TOUT, VEC)                                                                                                              \
+    do {                                                                                                                                        \
+        if (shared > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_chain_kernel<TOUT, VEC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared); \
+        tt_launch_pdl(add_rmsnorm_chain_kernel<TOUT, VEC>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, post_weight, post_offset, post_eps, results, (size_t)result_stride, index, depth_weights, weight, weight_offset, eps, (TOUT*)out, rows, hidden); \
+    } while (0)
     if (out_dtype == TT_F32) {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_chain_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        tt_launch_pdl(add_rmsnorm_chain_kernel<float>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, post_weight, post_offset, post_eps, results, (size_t)result_stride, index, depth_weights, weight, weight_offset, eps, (float*)out, rows, hidden);
+        if (wide) TT_CHAIN_LAUNCH(float, 4); else TT_CHAIN_LAUNCH(float, 1);
     } else {
-        if (shared > 48 * 1024) cudaFuncSetAttribute(add_rmsnorm_chain_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
-        tt_launch_pdl(add_rmsnorm_chain_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), shared, stream, residual, delta, splits, (size_t)split_stride, post_weight, post_offset, post_eps, results, (size_t)result_stride, index, depth_weights, weight, weight_offset, eps, (__nv_bfloat16*)out, rows, hidden);
+        if (wide) TT_CHAIN_LAUNCH(__nv_bfloat16, 4); else TT_CHAIN_LAUNCH(__nv_bfloat16, 1);
     }
+#undef TT_CHAIN_LAUNCH
     TT_LAUNCH_CHECK();
 }

@@ -215,43 +215,44 @@ def test_differential_attention(heads, kv_heads, dim, vdim, act_dtype):
 
     scale, lam, gain, eps = 0.3, 0.65, 0.45, 1e-5
     lengths = [300, 1, 65]
-    news = [3, 1, 2]                                         # the rows asked for: each sequence's last tokens
-    pools = Pools(3, 320, kv_heads, 2 * dim, vdim, act_dtype, 21)
-    keys = [randn(n, kv_heads, 2 * dim, seed=22 + b) for b, n in enumerate(lengths)]
-    values = [randn(n, kv_heads, vdim, seed=25 + b) for b, n in enumerate(lengths)]
-    q = randn(sum(news), heads, 2 * dim, seed=28)
-    mark_one, mark_two = randn(dim, seed=29, scale=3.0), randn(dim, seed=30, scale=3.0)
-    keys[0][49, :, :dim] = mark_one
-    keys[0][70, :, dim:] = mark_two
-    q[2, :, :dim] = mark_one * 2.0
-    q[2, :, dim:] = mark_two * 2.0
-    for b, n in enumerate(lengths):
-        for p in range(n):
-            pools.put(b, p, keys[b][p], values[b][p])
-    before = [n - c for n, c in zip(lengths, news)]
-    n_rows = sum(news)
-    out = torch.empty(n_rows, heads * vdim, dtype=act_dtype, device=DEV)
-    status = torch.zeros(1, dtype=torch.int32, device=DEV)
-    tol = 2e-5 if act_dtype == torch.float32 else 3e-2
-    qd = q.to(act_dtype)
-    for splits in (1, 2, 5):
-        part_acc = torch.empty(n_rows * heads * splits * 2 * vdim, dtype=torch.float32, device=DEV)
-        part_ml = torch.empty(n_rows * heads * splits * 4, dtype=torch.float32, device=DEV)
-        out.fill_(7.0)
-        api.differential_attention(qd.view(n_rows, -1).to(DEV), pools.k, pools.v, pools.table, cu_of(news), ints(before), 3, n_rows, heads,
-                                   kv_heads, dim, vdim, scale, lam, gain, eps, splits, out, part_acc, part_ml, status)
-        t = 0
-        for b, (c, start) in enumerate(zip(news, before)):
-            kb = torch.stack([pools.key(b, p) for p in range(lengths[b])])
-            vb = torch.stack([pools.value(b, p) for p in range(lengths[b])])
-            for i in range(start, start + c):
-                for h in range(heads):
-                    want = plain_differential(qd[t].double(), kb, vb, i, h, heads // kv_heads, dim, scale, lam, gain, eps)
-                    got = out[t].double().cpu().view(heads, vdim)[h]
-                    assert float((got - want).abs().max()) <= tol, (splits, b, i, h)
-                t += 1
-        # the marked keys carry their maps: without them the row differs by far more than the tolerance
-    assert int(status.item()) == 0
+    # the rows asked for: each sequence's last tokens; then one token a sequence, as a decoding step brings them
+    for news in ([3, 1, 2], [1, 1, 1]):
+        pools = Pools(3, 320, kv_heads, 2 * dim, vdim, act_dtype, 21)
+        keys = [randn(n, kv_heads, 2 * dim, seed=22 + b) for b, n in enumerate(lengths)]
+        values = [randn(n, kv_heads, vdim, seed=25 + b) for b, n in enumerate(lengths)]
+        q = randn(sum(news), heads, 2 * dim, seed=28)
+        mark_one, mark_two = randn(dim, seed=29, scale=3.0), randn(dim, seed=30, scale=3.0)
+        keys[0][49, :, :dim] = mark_one
+        keys[0][70, :, dim:] = mark_two
+        q[news[0] - 1, :, :dim] = mark_one * 2.0
+        q[news[0] - 1, :, dim:] = mark_two * 2.0
+        for b, n in enumerate(lengths):
+            for p in range(n):
+                pools.put(b, p, keys[b][p], values[b][p])
+        before = [n - c for n, c in zip(lengths, news)]
+        n_rows = sum(news)
+        out = torch.empty(n_rows, heads * vdim, dtype=act_dtype, device=DEV)
+        status = torch.zeros(1, dtype=torch.int32, device=DEV)
+        tol = 2e-5 if act_dtype == torch.float32 else 3e-2
+        qd = q.to(act_dtype)
+        for splits in (1, 2, 5):
+            part_acc = torch.empty(n_rows * heads * splits * 2 * vdim, dtype=torch.float32, device=DEV)
+            part_ml = torch.empty(n_rows * heads * splits * 4, dtype=torch.float32, device=DEV)
+            out.fill_(7.0)
+            api.differential_attention(qd.view(n_rows, -1).to(DEV), pools.k, pools.v, pools.table, cu_of(news), ints(before), 3, n_rows, heads,
+                                       kv_heads, dim, vdim, scale, lam, gain, eps, splits, out, part_acc, part_ml, status)
+            t = 0
+            for b, (c, start) in enumerate(zip(news, before)):
+                kb = torch.stack([pools.key(b, p) for p in range(lengths[b])])
+                vb = torch.stack([pools.value(b, p) for p in range(lengths[b])])
+                for i in range(start, start + c):
+                    for h in range(heads):
+                        want = plain_differential(qd[t].double(), kb, vb, i, h, heads // kv_heads, dim, scale, lam, gain, eps)
+                        got = out[t].double().cpu().view(heads, vdim)[h]
+                        assert float((got - want).abs().max()) <= tol, (news, splits, b, i, h)
+                    t += 1
+            # the marked keys carry their maps: without them the row differs by far more than the tolerance
+        assert int(status.item()) == 0
 
 
 # ---------------------------------------------------------------------------------- window attention with pooled blocks
@@ -350,12 +351,16 @@ def test_pooled_window_attention(heads, kv_heads, dim, window, pool, cap, act_dt
             km[1][n], vm[1][n] = coarse.key(1, n), coarse.value(1, n)
         query = (mark * 3.0).expand(heads, dim).to(act_dtype)
         one = torch.empty(1, heads * dim, dtype=act_dtype, device=DEV)
-        api.pooled_window_attention(query.reshape(1, -1).to(DEV), pools.k, pools.v, pools.table[1:].contiguous(), coarse.k, coarse.v,
-                                    coarse.table[1:].contiguous(), pool, cu_of([1]), ints([last]), 1, 1, heads, kv_heads, dim, scale, cap, window,
-                                    1, one, None, None, status)
-        for h in range(heads):
-            want = plain_pooled_row(query.double(), kb1, vb1, km[1], vm[1], last, h, heads // kv_heads, window, pool, scale, cap)
-            # the marked value is large: bfloat16 rounds an output of that size by up to half a unit in its last place
-            assert float((one[0].double().cpu().view(heads, dim)[h] - want).abs().max()) <= tol * max(1.0, float(want.abs().max())), (name, position, h)
+        for splits in (1, 4):       # a decoding step, its keys whole and in slices
+            part_acc = torch.empty(heads * splits * dim, dtype=torch.float32, device=DEV)
+            part_ml = torch.empty(heads * splits * 2, dtype=torch.float32, device=DEV)
+            one.fill_(7.0)
+            api.pooled_window_attention(query.reshape(1, -1).to(DEV), pools.k, pools.v, pools.table[1:].contiguous(), coarse.k, coarse.v,
+                                        coarse.table[1:].contiguous(), pool, cu_of([1]), ints([last]), 1, 1, heads, kv_heads, dim, scale, cap, window,
+                                        splits, one, part_acc, part_ml, status)
+            for h in range(heads):
+                want = plain_pooled_row(query.double(), kb1, vb1, km[1], vm[1], last, h, heads // kv_heads, window, pool, scale, cap)
+                # the marked value is large: bfloat16 rounds an output of that size by up to half a unit in its last place
+                assert float((one[0].double().cpu().view(heads, dim)[h] - want).abs().max()) <= tol * max(1.0, float(want.abs().max())), (name, position, splits, h)
         kb[1], vb[1] = kb1, vb1
     assert int(status.item()) == 0

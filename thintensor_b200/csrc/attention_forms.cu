@@ -369,9 +369,8 @@ __device__ __forceinline__ void fm_cp16(void* smem_dst, const void* src) {
 __device__ __forceinline__ void fm_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void fm_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-constexpr int FM_TILES = 4;             // 16-row tiles of a CTA
-
-template <int KD, int VD, int MAPS> struct FormShape {
+// TILES: 16-row tiles of a CTA; 4 for prompts, 1 for steps of one token a sequence (more CTAs fit an SM, each with a slice of the keys)
+template <int KD, int VD, int MAPS, int TILES> struct FormShape {
     static_assert(KD % 16 == 0 && VD % 8 == 0, "score dimensions in halves of a 32-wide chunk, value dimensions in 8-wide tiles");
     static constexpr int KC = KD / 32;                          // whole 32-wide chunks of a map's score dimensions
     static constexpr bool HALF = (KD % 32) != 0;                // and a last chunk of 16
@@ -382,8 +381,8 @@ template <int KD, int VD, int MAPS> struct FormShape {
     static constexpr int V_TILE = VD * 128;
     static constexpr int STAGE = K_TILE + V_TILE;
     static constexpr int STAGES = STAGE <= 16384 ? 3 : 2;
-    static constexpr int THREADS = FM_TILES * MAPS * 32;
-    static constexpr int EXCHANGE = MAPS == 2 ? FM_TILES * 16 * VD * 4 : 0;    // map 2's output on its way to map 1's warps
+    static constexpr int THREADS = TILES * MAPS * 32;
+    static constexpr int EXCHANGE = MAPS == 2 ? TILES * 16 * VD * 4 : 0;    // map 2's output on its way to map 1's warps
     static constexpr int SHARED = STAGES * STAGE > EXCHANGE ? STAGES * STAGE : EXCHANGE;
 };
 
@@ -493,19 +492,19 @@ struct FormArgs {
     unsigned* status;
 };
 
-template <int KD, int VD, int MAPS, bool POOLED>
-__global__ void __launch_bounds__(FormShape<KD, VD, MAPS>::THREADS)
+template <int KD, int VD, int MAPS, bool POOLED, int TILES>
+__global__ void __launch_bounds__(FormShape<KD, VD, MAPS, TILES>::THREADS)
 form_kernel(const FormArgs a) {
-    using S = FormShape<KD, VD, MAPS>;
+    using S = FormShape<KD, VD, MAPS, TILES>;
     constexpr int KC = S::KC, NT = S::NT, STAGES = S::STAGES, ROW = MAPS * KD;
     extern __shared__ uint4 form_stage_mem[];                  // [STAGES][K tile, V tile]; at the end map 2's output
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, t = lane & 3;
-    const int my_tile = warp & (FM_TILES - 1), map = warp / FM_TILES;
+    const int my_tile = warp & (TILES - 1), map = warp / TILES;
     const int kh = blockIdx.x;
     const int group = a.heads / a.kv_heads;
-    const int tokens_per_cta = a.tokens_per_tile * FM_TILES;
+    const int tokens_per_cta = a.tokens_per_tile * TILES;
 
     // which sequence and which of its CTA tiles; late tiles of a sequence come first
     int tile = a.cta_tiles - 1 - (int)blockIdx.y;
@@ -722,10 +721,10 @@ form_kernel(const FormArgs a) {
 #define FM_DIFFERENTIAL_SHAPES(X) X(32, 64) X(48, 96) X(64, 128) X(64, 64) X(128, 128)
 #define FM_POOLED_SHAPES(X) X(32) X(64) X(96) X(128)
 
-template <int KD, int VD, int MAPS, bool POOLED>
-int form_launch(FormArgs a, int n_tokens, cudaStream_t stream) {
-    using S = FormShape<KD, VD, MAPS>;
-    auto kernel = form_kernel<KD, VD, MAPS, POOLED>;
+template <int KD, int VD, int MAPS, bool POOLED, int TILES>
+int form_launch_tiles(FormArgs a, int n_tokens, cudaStream_t stream) {
+    using S = FormShape<KD, VD, MAPS, TILES>;
+    auto kernel = form_kernel<KD, VD, MAPS, POOLED, TILES>;
     static bool configured = false;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, S::SHARED);
@@ -733,10 +732,16 @@ int form_launch(FormArgs a, int n_tokens, cudaStream_t stream) {
         configured = true;
     }
     a.tokens_per_tile = 16 / (a.heads / a.kv_heads);
-    const int tokens_per_cta = a.tokens_per_tile * FM_TILES;
+    const int tokens_per_cta = a.tokens_per_tile * TILES;
     a.cta_tiles = (n_tokens + tokens_per_cta - 1) / tokens_per_cta + a.sequences;       // upper bound; spare CTAs leave at once
     if (a.cta_tiles > 65535 || a.kv_heads > 65535 || a.splits > 65535) return (int)cudaErrorInvalidValue;
     return (int)tt_launch_pdl(kernel, dim3(a.kv_heads, a.cta_tiles, a.splits), dim3(S::THREADS), S::SHARED, stream, a);
+}
+
+template <int KD, int VD, int MAPS, bool POOLED>
+int form_launch(const FormArgs& a, int n_tokens, cudaStream_t stream) {
+    if (n_tokens == a.sequences) return form_launch_tiles<KD, VD, MAPS, POOLED, 1>(a, n_tokens, stream);     // one token a sequence
+    return form_launch_tiles<KD, VD, MAPS, POOLED, 4>(a, n_tokens, stream);
 }
 
 // 0: done (or an error code); -1: sizes that the tensor-core kernel does not take
@@ -753,6 +758,19 @@ int form_pooled(const FormArgs& a, int head_dim, int n_tokens, cudaStream_t stre
     return -1;
 }
 }  // namespace
+
+// Whether the tensor-core kernels take these sizes in bfloat16: maps != 0 asks about differential attention (dim numbers a
+// map), maps == 0 about window attention with pooled blocks (value_dim == dim).
+extern "C" int tt_attention_forms_on_tensor_cores(int maps, int heads, int kv_heads, int dim, int value_dim) {
+    if (kv_heads <= 0 || heads % kv_heads || heads / kv_heads > 16) return 0;
+#define X(KD_, VD_) if (maps && dim == KD_ && value_dim == VD_) return 1;
+    FM_DIFFERENTIAL_SHAPES(X)
+#undef X
+#define X(HD_) if (!maps && dim == HD_ && value_dim == HD_) return 1;
+    FM_POOLED_SHAPES(X)
+#undef X
+    return 0;
+}
 
 extern "C" int tt_differential_attention(const void* q, const void* k_pool, const void* v_pool, int dtype, const int* table,
                                          int table_width, int pool_blocks, const int* cu, const int* len_before, int sequences,

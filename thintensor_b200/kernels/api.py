@@ -500,6 +500,16 @@ def differential_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.
               _ptr(status), _stream()), "differential_attention", 2 if splits > 1 else 1)
 
 
+def attention_forms_on_tensor_cores(dtype: torch.dtype, differential: bool, heads: int, kv_heads: int, dim: int, value_dim: int) -> bool:
+    """Whether differential attention (``dim`` numbers a map) or window attention with pooled blocks (``value_dim == dim``)
+    runs on tensor cores at these sizes: bfloat16, and a size the kernels are built for; its parallel unit is then a
+    (sequence, key/value head) pair and not a (token, query head) row."""
+    if dtype != torch.bfloat16:
+        return False
+    fn = _fn("attention_forms", "tt_attention_forms_on_tensor_cores", [c_int, c_int, c_int, c_int, c_int])
+    return bool(fn(1 if differential else 0, heads, kv_heads, dim, value_dim))
+
+
 def pool_blocks(k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, mean_k: torch.Tensor, mean_v: torch.Tensor,
                 mean_table: torch.Tensor, cu: torch.Tensor, len_before: torch.Tensor, sequences: int, most_blocks: int, kv_heads: int,
                 head_dim: int, value_dim: int, every: int, status: torch.Tensor) -> None:

@@ -107,7 +107,10 @@ class DifferentialAttention(Mixer):
                                 cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                                 self.heads, self.kv_heads, row, self.value_dim, ctx.status, q_gain=self.q_gain)
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, self.heads * self.value_dim))
-        splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
+        if api.attention_forms_on_tensor_cores(q.dtype, True, self.heads, self.kv_heads, self.dim, self.value_dim):
+            splits = kv_splits(ctx, ctx.n_tokens * self.kv_heads, 128, 3 * api.sm_count(q.device))
+        else:
+            splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
         part_acc, part_ml = _slice_scratch(ctx, "differential", ctx.n_tokens * self.heads, splits, self.value_dim, maps=2)
         api.differential_attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                                    self.kv_heads, self.dim, self.value_dim, self.scale, self.lam, 1.0 - self.diff, self.eps, splits, mixed,
@@ -181,7 +184,10 @@ class PooledWindowAttention(Mixer):
         splits = 1
         if ctx.decode:      # the keys a position sees: its window and the blocks before it
             most = self.window + ctx.max_total // self.pool
-            splits = max(1, min(8 * api.sm_count(q.device) // max(ctx.n_tokens * self.heads, 1), most // 256, 64))
+            if api.attention_forms_on_tensor_cores(q.dtype, False, self.heads, self.kv_heads, self.dim, self.dim):
+                splits = max(1, min(3 * api.sm_count(q.device) // max(ctx.n_tokens * self.kv_heads, 1), most // 128, 64))
+            else:
+                splits = max(1, min(8 * api.sm_count(q.device) // max(ctx.n_tokens * self.heads, 1), most // 256, 64))
         part_acc, part_ml = _slice_scratch(ctx, "window", ctx.n_tokens * self.heads, splits, self.dim)
         api.pooled_window_attention(q, cache.k_pool, cache.v_pool, table, coarse.k_pool, coarse.v_pool, mean_table, self.pool, ctx.cu,
                                     ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.kv_heads, self.dim, self.scale,

@@ -55,6 +55,7 @@ class DifferentialAttention(Mixer):
         self.projection: Linear | None = None       # q (and k, v where the layer has its own)
         self.out: Linear | None = None
         self.no_rotation: torch.Tensor | None = None
+        self.on_tensor_cores: bool | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
         n = self.names
@@ -107,7 +108,9 @@ class DifferentialAttention(Mixer):
                                 cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                                 self.heads, self.kv_heads, row, self.value_dim, ctx.status, q_gain=self.q_gain)
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, self.heads * self.value_dim))
-        if api.attention_forms_on_tensor_cores(q.dtype, True, self.heads, self.kv_heads, self.dim, self.value_dim):
+        if self.on_tensor_cores is None:        # asked once: the answer depends on the sizes and the activations' type only
+            self.on_tensor_cores = api.attention_forms_on_tensor_cores(q.dtype, True, self.heads, self.kv_heads, self.dim, self.value_dim)
+        if self.on_tensor_cores:
             splits = kv_splits(ctx, ctx.n_tokens * self.kv_heads, 128, 3 * api.sm_count(q.device))
         else:
             splits = kv_splits(ctx, ctx.n_tokens * self.heads, 256, 8 * api.sm_count(q.device))
@@ -137,6 +140,7 @@ class PooledWindowAttention(Mixer):
         self.projection: Linear | None = None       # q, then k
         self.out: Linear | None = None
         self.no_rotation: torch.Tensor | None = None
+        self.on_tensor_cores: bool | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
         n = self.names
@@ -184,7 +188,9 @@ class PooledWindowAttention(Mixer):
         splits = 1
         if ctx.decode:      # the keys a position sees: its window and the blocks before it
             most = self.window + ctx.max_total // self.pool
-            if api.attention_forms_on_tensor_cores(q.dtype, False, self.heads, self.kv_heads, self.dim, self.dim):
+            if self.on_tensor_cores is None:        # asked once: the answer depends on the sizes and the activations' type only
+                self.on_tensor_cores = api.attention_forms_on_tensor_cores(q.dtype, False, self.heads, self.kv_heads, self.dim, self.dim)
+            if self.on_tensor_cores:
                 splits = max(1, min(3 * api.sm_count(q.device) // max(ctx.n_tokens * self.kv_heads, 1), most // 128, 64))
             else:
                 splits = max(1, min(8 * api.sm_count(q.device) // max(ctx.n_tokens * self.heads, 1), most // 256, 64))

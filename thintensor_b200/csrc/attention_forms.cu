@@ -342,8 +342,7 @@ __global__ void pooled_window_rows_kernel(const T* __restrict__ q, const T* __re
 // logarithm units, for the same merge kernels.
 
 __device__ __forceinline__ void fm_mma(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
-    asm volatile(
-        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
@@ -402,17 +401,23 @@ __device__ __forceinline__ void form_block_math(FormState<KD, VD>& st, int index
     constexpr int KC = KD / 32, NT = VD / 8;
     constexpr bool HALF = (KD % 32) != 0;
     constexpr float LOG2E = 1.4426950408889634f;
+    // the eight score tiles take turns, so that consecutive products do not wait for one another's accumulator
     float s[8][4];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-        s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
+    for (int j = 0; j < 8; ++j) s[j][0] = s[j][1] = s[j][2] = s[j][3] = 0.0f;
 #pragma unroll
-        for (int c = 0; c < KC; ++c) {
-            const uint4 kr = load_k(j, c);
-            fm_mma(s[j], st.qa[c][0], st.qb[c][0], st.qa[c][1], st.qb[c][1], kr.x, kr.y);
-            fm_mma(s[j], st.qa[c][2], st.qb[c][2], st.qa[c][3], st.qb[c][3], kr.z, kr.w);
-        }
-        if constexpr (HALF) {
+    for (int c = 0; c < KC; ++c) {
+        uint4 kr[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) kr[j] = load_k(j, c);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) fm_mma(s[j], st.qa[c][0], st.qb[c][0], st.qa[c][1], st.qb[c][1], kr[j].x, kr[j].y);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) fm_mma(s[j], st.qa[c][2], st.qb[c][2], st.qa[c][3], st.qb[c][3], kr[j].z, kr[j].w);
+    }
+    if constexpr (HALF) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
             const uint2 kr = load_k_half(j);
             fm_mma(s[j], st.qa[KC][0], st.qb[KC][0], st.qa[KC][1], st.qb[KC][1], kr.x, kr.y);
         }
@@ -466,13 +471,21 @@ __device__ __forceinline__ void form_block_math(FormState<KD, VD>& st, int index
         pa[mm][2] = fm_pack(s[2 * mm + 1][0], s[2 * mm + 1][1]);
         pa[mm][3] = fm_pack(s[2 * mm + 1][2], s[2 * mm + 1][3]);
     }
+    // likewise the output tiles, four at a time
 #pragma unroll
-    for (int n = 0; n < NT; ++n) {
+    for (int half = 0; half < 2; ++half) {
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const uint4 vr = load_v(n, half);
-            fm_mma(st.o[n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr.x, vr.y);
-            fm_mma(st.o[n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr.z, vr.w);
+        for (int n0 = 0; n0 < NT; n0 += 4) {
+            uint4 vr[4];
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+                if (n0 + n < NT) vr[n] = load_v(n0 + n, half);
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+                if (n0 + n < NT) fm_mma(st.o[n0 + n], pa[2 * half][0], pa[2 * half][1], pa[2 * half][2], pa[2 * half][3], vr[n].x, vr[n].y);
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+                if (n0 + n < NT) fm_mma(st.o[n0 + n], pa[2 * half + 1][0], pa[2 * half + 1][1], pa[2 * half + 1][2], pa[2 * half + 1][3], vr[n].z, vr[n].w);
         }
     }
 }

@@ -195,6 +195,8 @@ __global__ void differential_merge_kernel(const float* __restrict__ part_acc, co
     differential_write<T>(a1, l1, a2, l2, lambda, gain, eps, value_dim, lane, out + (size_t)row * value_dim);
 }
 
+constexpr int POOL_RUN = 256;       // tokens whose places in the cache pool_blocks_kernel looks up together
+
 // Means of the blocks that this step completes: block n of sequence b (tokens n * every .. n * every + every - 1) for
 // floor(before / every) <= n < floor(after / every).  grid (blocks a sequence may complete, kv heads, sequences).
 template <typename T>
@@ -215,20 +217,46 @@ __global__ void pool_blocks_kernel(const T* __restrict__ k_pool, const T* __rest
     const long long v_dst = tt_value_offset(mean_row, n, kh, kv_heads, value_dim, mean_blocks, status);
     if (k_dst < 0 || v_dst < 0) return;
     const float share = 1.0f / (float)every;
-    for (int d = threadIdx.x; d < head_dim + value_dim; d += blockDim.x) {
-        float sum = 0.0f;
-        for (int j = 0; j < every; ++j) {
-            const int position = n * every + j;
-            if (d < head_dim) {
-                const long long off = tt_cache_offset(table_row, position, kh, kv_heads, head_dim, pool_blocks, status);
-                if (off >= 0) sum += tt_to_float(k_pool[off + d]);
-            } else {
-                const long long off = tt_value_offset(table_row, position, kh, kv_heads, value_dim, pool_blocks, status);
-                if (off >= 0) sum += tt_to_float(v_pool[off + (long long)(d - head_dim) * TT_BLOCK_TOKENS]);
-            }
+    // the block's tokens in runs of POOL_RUN: their places in the cache are found once a run, side by side, and every
+    // thread then adds its dimension over the run in token order with independent loads
+    __shared__ long long k_at[POOL_RUN], v_at[POOL_RUN];
+    constexpr int MOST = (2 * ATTN_MAX_HEAD_DIM + 127) / 128;      // dimensions a thread may own (blocks of at least 128 threads)
+    float sum[MOST];
+#pragma unroll
+    for (int i = 0; i < MOST; ++i) sum[i] = 0.0f;
+    for (int j0 = 0; j0 < every; j0 += POOL_RUN) {
+        const int count = min(POOL_RUN, every - j0);
+        __syncthreads();
+        for (int j = threadIdx.x; j < count; j += blockDim.x) {
+            const int position = n * every + j0 + j;
+            k_at[j] = tt_cache_offset(table_row, position, kh, kv_heads, head_dim, pool_blocks, status);
+            v_at[j] = tt_value_offset(table_row, position, kh, kv_heads, value_dim, pool_blocks, status);
         }
-        if (d < head_dim) mean_k[k_dst + d] = tt_from_float<T>(sum * share);
-        else mean_v[v_dst + (long long)(d - head_dim) * TT_BLOCK_TOKENS] = tt_from_float<T>(sum * share);
+        __syncthreads();
+#pragma unroll
+        for (int i = 0; i < MOST; ++i) {
+            const int d = threadIdx.x + i * blockDim.x;
+            if (d >= head_dim + value_dim) break;
+            float acc = sum[i];
+            if (d < head_dim) {
+#pragma unroll 8
+                for (int j = 0; j < count; ++j)
+                    if (k_at[j] >= 0) acc += tt_to_float(k_pool[k_at[j] + d]);
+            } else {
+                const long long step = (long long)(d - head_dim) * TT_BLOCK_TOKENS;
+#pragma unroll 8
+                for (int j = 0; j < count; ++j)
+                    if (v_at[j] >= 0) acc += tt_to_float(v_pool[v_at[j] + step]);
+            }
+            sum[i] = acc;
+        }
+    }
+#pragma unroll
+    for (int i = 0; i < MOST; ++i) {
+        const int d = threadIdx.x + i * blockDim.x;
+        if (d >= head_dim + value_dim) break;
+        if (d < head_dim) mean_k[k_dst + d] = tt_from_float<T>(sum[i] * share);
+        else mean_v[v_dst + (long long)(d - head_dim) * TT_BLOCK_TOKENS] = tt_from_float<T>(sum[i] * share);
     }
 }
 

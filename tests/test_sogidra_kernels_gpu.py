@@ -270,7 +270,8 @@ def plain_pooled_row(q, keys, values, key_means, value_means, i, h, group, windo
 @pytest.mark.parametrize("act_dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,window,pool,cap", [(4, 2, 40, 21, 5, 8.0), (2, 2, 16, 70, 64, 0.0), (3, 1, 8, 1, 1, 3.0),
                                                                 (2, 1, 72, 9, 30, 30.0), (4, 2, 128, 100, 16, 20.0), (2, 1, 64, 33, 8, 0.0),
-                                                                (6, 3, 96, 70, 11, 15.0), (16, 1, 32, 64, 64, 5.0)])
+                                                                (6, 3, 96, 70, 11, 15.0), (16, 1, 32, 64, 64, 5.0), (2, 2, 32, 1, 1, 0.0),
+                                                                (4, 1, 64, 9, 30, 6.0), (2, 1, 128, 130, 3, 0.0)])
 def test_pooled_window_attention(heads, kv_heads, dim, window, pool, cap, act_dtype):
     """The cache is filled in steps (portions of a prompt, then single tokens); after each step the blocks it completed
     must have their means in the coarser cache and no others.  Every position's row is then compared with the plain

@@ -14,6 +14,9 @@
 //   that a step completes, from the token cache, right after the step's keys were appended.
 //
 // The slices' partial (max, sum, accumulator) triples are merged in slice order, so a result does not depend on the grid.
+//
+// bfloat16 at the sizes listed near the end of this file runs both forms on tensor cores instead (form_kernel); the
+// kernels below are the float32 path and take every other size.
 #include "attention_kernels.cuh"
 
 namespace {
@@ -356,7 +359,7 @@ __global__ void pooled_window_rows_kernel(const T* __restrict__ q, const T* __re
 // Both forms for bfloat16 on tensor cores (mma.sync m16n8k16, float32 accumulators and softmax), prompts and decoding.
 //
 // A CTA owns 64 query rows of one sequence and one key/value head, four tiles of 16 rows ((token, head of the group)
-// pairs), and a slice of the blocks of 64 keys that those rows see.  Every block's K and V tiles are copied once per CTA
+// pairs; one tile in a step of one token a sequence), and a slice of the blocks of 64 keys that those rows see.  Every block's K and V tiles are copied once per CTA
 // into shared memory with cp.async, one or two blocks ahead.  With two maps a second set of four warps owns the same rows
 // for map 2: it reads the other half of the query and key rows and the same value tile, so that a warp's arithmetic is that
 // of an ordinary head with KD score dimensions and VD value dimensions, and the two sets meet in shared memory at the end

@@ -1,6 +1,7 @@
 // Causal grouped-query attention over the block cache, for any key size and any value size
 // up to 256 (the two may differ), in float32 or bfloat16 storage with float32 arithmetic,
-// optionally with a per-head sink term in the softmax denominator.
+// optionally with a per-head sink term in the softmax denominator, capped scores, a bias that grows with the
+// distance between query and key (a slope per head), and a sigmoid gate on the output (see AttnExtra).
 // One kernel serves prompts and decoding: a warp owns one (token, query head, split)
 // and walks that token's visible keys 32 at a time with a running softmax; with more
 // than one split the partial (max, sum, accumulator) triples are merged by a second
@@ -19,7 +20,9 @@ extern "C" int tt_attention(const void* q, const void* k_pool, const void* v_poo
                             int table_width, int pool_blocks, const int* cu, const int* len_before, int sequences,
                             int n_tokens, int heads, int kv_heads, int head_dim, int value_dim, float scale, const float* sinks,
                             int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* status,
-                            cudaStream_t stream) {
+                            float softcap, const float* slopes, const float* gate, int gate_splits, long long gate_split_stride,
+                            int gate_row, int gate_per_head, cudaStream_t stream) {
+    const AttnExtra extra{softcap, slopes, gate, gate_splits, gate_split_stride, gate_row, gate_per_head};
     if (n_tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > ATTN_MAX_HEAD_DIM || value_dim <= 0 || value_dim > ATTN_MAX_HEAD_DIM || heads % kv_heads || splits < 1 || splits > 65535)
         return (int)cudaErrorInvalidValue;
@@ -28,13 +31,13 @@ extern "C" int tt_attention(const void* q, const void* k_pool, const void* v_poo
     const dim3 grid((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS), (unsigned)splits);
     const size_t shared = (size_t)ATTN_WARPS * head_dim * sizeof(float);
     if (dtype == TT_F32) {
-        attention_rows_kernel<float><<<grid, ATTN_WARPS * 32, shared, stream>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (float*)out, part_acc, part_ml, status);
+        attention_rows_kernel<float><<<grid, ATTN_WARPS * 32, shared, stream>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (float*)out, part_acc, part_ml, status, extra);
         if (splits > 1)
-            attention_merge_kernel<float><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (float*)out);
+            attention_merge_kernel<float><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (float*)out, extra, heads);
     } else {
-        attention_rows_kernel<__nv_bfloat16><<<grid, ATTN_WARPS * 32, shared, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
+        attention_rows_kernel<__nv_bfloat16><<<grid, ATTN_WARPS * 32, shared, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status, extra);
         if (splits > 1)
-            attention_merge_kernel<__nv_bfloat16><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (__nv_bfloat16*)out);
+            attention_merge_kernel<__nv_bfloat16><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (__nv_bfloat16*)out, extra, heads);
     }
     TT_LAUNCH_CHECK();
 }

@@ -896,7 +896,7 @@ extern "C" int tt_pooled_window_attention(const void* q, const void* k_pool, con
         if (code > 0) return code;
         if (code == 0) {
             if (splits > 1)
-                tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (__nv_bfloat16*)out);
+                tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (__nv_bfloat16*)out, AttnExtra{}, heads);
             TT_LAUNCH_CHECK();
         }
     }
@@ -904,11 +904,11 @@ extern "C" int tt_pooled_window_attention(const void* q, const void* k_pool, con
     if (dtype == TT_F32) {
         tt_launch_pdl(pooled_window_rows_kernel<float>, grid, dim3(ATTN_WARPS * 32), shared, stream, (const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, (const float*)mean_k, (const float*)mean_v, mean_table, mean_width, mean_blocks, every, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, scale, cap, window, splits, (float*)out, part_acc, part_ml, status);
         if (splits > 1)
-            tt_launch_pdl(attention_merge_kernel<float>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (float*)out);
+            tt_launch_pdl(attention_merge_kernel<float>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (float*)out, AttnExtra{}, heads);
     } else {
         tt_launch_pdl(pooled_window_rows_kernel<__nv_bfloat16>, grid, dim3(ATTN_WARPS * 32), shared, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, (const __nv_bfloat16*)mean_k, (const __nv_bfloat16*)mean_v, mean_table, mean_width, mean_blocks, every, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, scale, cap, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
         if (splits > 1)
-            tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (__nv_bfloat16*)out);
+            tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3(grid.x), dim3(ATTN_WARPS * 32), 0, stream, (const float*)part_acc, (const float*)part_ml, splits, head_dim, rows, (__nv_bfloat16*)out, AttnExtra{}, heads);
     }
     TT_LAUNCH_CHECK();
 }

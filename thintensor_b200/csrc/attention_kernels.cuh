@@ -51,6 +51,29 @@ __device__ __forceinline__ float dot16<__nv_bfloat16>(const __nv_bfloat16* __res
     return acc;
 }
 
+// Options of the exact kernels that most callers leave at zero (none).
+//   softcap > 0: a scaled score s becomes softcap * tanh(s / softcap).
+//   slopes (float32, one per query head): slope_h * (query position - key position) is taken off the (capped) score.
+//   gate: float32 partial sums [gate_splits][tokens][gate_row] (the pointer stands at the gate's first column); the
+//   output is multiplied by sigmoid(gate), one number per output number (column h * value_dim + d) or, with
+//   gate_per_head, one per head (column h).
+struct AttnExtra {
+    float softcap;
+    const float* slopes;
+    const float* gate;
+    int gate_splits;
+    long long gate_split_stride;
+    int gate_row;
+    int gate_per_head;
+};
+
+__device__ __forceinline__ float attn_gate(const AttnExtra& x, int t, int h, int value_dim, int d) {
+    const float* g = x.gate + (size_t)t * x.gate_row + (x.gate_per_head ? h : h * value_dim + d);
+    float z = 0.0f;
+    for (int s = 0; s < x.gate_splits; ++s) z += __ldg(g + (size_t)s * x.gate_split_stride);
+    return 1.0f / (1.0f + expf(-z));
+}
+
 // window <= 0: all keys 0..pos.  window > 0: keys pos - window + 1 .. pos.
 // Keys have head_dim numbers, values value_dim (the output's width per head).
 // sinks (float32, one per query head, or null): the softmax denominator also holds exp(sink_h), a
@@ -62,7 +85,7 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
                                       int sequences, int n_tokens, int heads, int kv_heads, int head_dim, int value_dim,
                                       float scale, const float* __restrict__ sinks,
                                       int window, int splits, T* __restrict__ out, float* __restrict__ part_acc,
-                                      float* __restrict__ part_ml, unsigned* status) {
+                                      float* __restrict__ part_ml, unsigned* status, AttnExtra extra) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ float q_shared[];  // ATTN_WARPS * head_dim
@@ -89,6 +112,8 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 
     float m_run = -INFINITY, l_run = 0.0f;
     if (sinks && split == 0) { m_run = __ldg(sinks + h); l_run = 1.0f; }
+    const float slope = extra.slopes ? __ldg(extra.slopes + h) : 0.0f;
+    const float cap = extra.softcap, inv_cap = cap > 0.0f ? 1.0f / cap : 0.0f;
     float acc[ATTN_MAX_HEAD_DIM / 32];
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) acc[i] = 0.0f;
@@ -101,6 +126,8 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
             off = tt_cache_offset(table_row, key, kh, kv_heads, head_dim, pool_blocks, status);
             if (off >= 0) {
                 score = dot16<T>(k_pool + off, qs, head_dim);
+                if (cap > 0.0f) score = cap * tanhf(score * inv_cap);
+                score -= slope * (float)(pos - key);
                 voff = tt_value_offset(table_row, key, kh, kv_heads, value_dim, pool_blocks, nullptr);
             }
         }
@@ -132,7 +159,11 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
 #pragma unroll
         for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
             const int d = lane + 32 * i;
-            if (d < value_dim) out[((size_t)t * heads + h) * value_dim + d] = tt_from_float<T>(acc[i] * inv);
+            if (d < value_dim) {
+                float o = acc[i] * inv;
+                if (extra.gate) o *= attn_gate(extra, t, h, value_dim, d);
+                out[((size_t)t * heads + h) * value_dim + d] = tt_from_float<T>(o);
+            }
         }
     } else {
         const size_t slot = ((size_t)t * heads + h) * splits + split;
@@ -148,13 +179,15 @@ __global__ void attention_rows_kernel(const T* __restrict__ q, const T* __restri
     }
 }
 
-// out[t, h, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M), M = max_s m_s.
+// out[t, h, :] = sum_s acc_s * exp(m_s - M) / sum_s l_s * exp(m_s - M), M = max_s m_s, times the gate of `extra` if it
+// has one (row = t * heads + h; `heads` is read only then).
 // One warp per row.  Lanes first take one slice each to find M and the weights, then all
 // lanes walk the slices' accumulators with independent loads; the additions run in slice
 // order, so the result does not depend on the grid.
 template <typename T>
 __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                                       int splits, int head_dim, long long rows, T* __restrict__ out) {
+                                       int splits, int head_dim, long long rows, T* __restrict__ out, AttnExtra extra,
+                                       int heads) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -193,6 +226,10 @@ __global__ void attention_merge_kernel(const float* __restrict__ part_acc, const
 #pragma unroll
     for (int i = 0; i < ATTN_MAX_HEAD_DIM / 32; ++i) {
         const int d = lane + 32 * i;
-        if (d < head_dim) out[(size_t)row * head_dim + d] = tt_from_float<T>(acc[i] * inv);
+        if (d < head_dim) {
+            float o = acc[i] * inv;
+            if (extra.gate) o *= attn_gate(extra, (int)(row / heads), (int)(row % heads), head_dim, d);
+            out[(size_t)row * head_dim + d] = tt_from_float<T>(o);
+        }
     }
 }

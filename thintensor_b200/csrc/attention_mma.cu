@@ -920,7 +920,7 @@ int merge_slices(int n_rows_tokens, int heads, int splits, void* out, float* par
     if (splits > 1 && !inside_kernel) {
         const long long rows = (long long)n_rows_tokens * heads;
         tt_launch_pdl(attention_merge_kernel<__nv_bfloat16>, dim3((unsigned)((rows + ATTN_WARPS - 1) / ATTN_WARPS)), dim3(ATTN_WARPS * 32), 0, stream,
-            part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out);
+            part_acc, part_ml, splits, HD, rows, (__nv_bfloat16*)out, AttnExtra{}, heads);
     }
     return (int)cudaGetLastError();
 }

@@ -97,13 +97,13 @@ extern "C" int tt_attention_decode_static(const void* q, const void* k_pool, con
     const size_t shared = (size_t)ATTN_WARPS * head_dim * sizeof(float);
     // with one split the first kernel writes `out` directly and the scratch is not touched
     if (dtype == TT_F32) {
-        attention_rows_kernel<float><<<grid, ATTN_WARPS * 32, shared, stream>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (float*)out, part_acc, part_ml, status);
+        attention_rows_kernel<float><<<grid, ATTN_WARPS * 32, shared, stream>>>((const float*)q, (const float*)k_pool, (const float*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (float*)out, part_acc, part_ml, status, AttnExtra{});
         if (splits > 1)
-            attention_merge_kernel<float><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (float*)out);
+            attention_merge_kernel<float><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (float*)out, AttnExtra{}, heads);
     } else {
-        attention_rows_kernel<__nv_bfloat16><<<grid, ATTN_WARPS * 32, shared, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status);
+        attention_rows_kernel<__nv_bfloat16><<<grid, ATTN_WARPS * 32, shared, stream>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, sinks, window, splits, (__nv_bfloat16*)out, part_acc, part_ml, status, AttnExtra{});
         if (splits > 1)
-            attention_merge_kernel<__nv_bfloat16><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (__nv_bfloat16*)out);
+            attention_merge_kernel<__nv_bfloat16><<<grid.x, ATTN_WARPS * 32, 0, stream>>>(part_acc, part_ml, splits, value_dim, rows, (__nv_bfloat16*)out, AttnExtra{}, heads);
     }
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) snprintf(last_error, sizeof(last_error), "launch failed: %s", cudaGetErrorString(launched));

@@ -871,10 +871,11 @@ extern "C" int tt_embed_position_gather(const void* table, const void* positions
 
 // ------------------------------------------------------------------------------------
 // Ungated activation: act[t, j] = f(sum over slices of x[s][t, j]).  f by `activation`: 0 silu, 1 relu, 2 tanh-gelu (as
-// in tt_gate_activation), 3 xielu with two numbers a = softplus(p) and c = 1/2 + softplus(q) that the caller has formed:
+// in tt_gate_activation), 4 the exact gelu 0.5 z (1 + erf(z / sqrt 2)), 3 xielu with two numbers a = softplus(p) and c = 1/2 + softplus(q) that the caller has formed:
 //   z > 0: a z^2 + z / 2;   z <= 0: c (exp(z) - 1 - z) + z / 2     (expm1f keeps small z exact)
 // ------------------------------------------------------------------------------------
 __device__ __forceinline__ float tt_unary_activation(float z, int activation, float a, float c) {
+    if (activation == 4) return 0.5f * z * (1.0f + erff(z * 0.70710678118654752f));        // the exact gelu
     if (activation == 3) return z > 0.0f ? fmaf(a * z, z, 0.5f * z) : fmaf(c, expm1f(z) - z, 0.5f * z);
     return tt_gate_activation(z, activation);
 }
@@ -906,7 +907,7 @@ __global__ void activation_kernel(const float* __restrict__ x, int splits, size_
 extern "C" int tt_activation(const float* x, int splits, long long split_stride, void* act, int act_dtype, long long total,
                              int activation, float a, float c, cudaStream_t stream) {
     if (total <= 0) return 0;
-    if (activation < 0 || activation > 3 || (total & 3)) return (int)cudaErrorInvalidValue;     // rows of whole groups of four
+    if (activation < 0 || activation > 4 || (total & 3)) return (int)cudaErrorInvalidValue;     // rows of whole groups of four
     const int threads = 256;
     const unsigned blocks = (unsigned)((total / 4 + threads - 1) / threads);
     if (act_dtype == TT_F32)
@@ -1056,5 +1057,113 @@ extern "C" int tt_add_rmsnorm_chain(float* residual, const float* delta, int spl
         if (wide) TT_CHAIN_LAUNCH(__nv_bfloat16, 4); else TT_CHAIN_LAUNCH(__nv_bfloat16, 1);
     }
 #undef TT_CHAIN_LAUNCH
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// The stream takes a delta and is handed on narrowed: residual[r] += delta[0][r] + delta[1][r] + ... (fixed order; no delta:
+// nothing is added), out[r] = residual[r] in the activation dtype.  For a part that reads the stream itself, not a norm of it.
+// ------------------------------------------------------------------------------------
+template <typename TOut>
+__global__ void add_narrow_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
+                                  TOut* __restrict__ out, size_t total) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float x = residual[i];
+    if (splits > 0) {
+        for (int s = 0; s < splits; ++s) x += __ldg(delta + s * split_stride + i);
+        residual[i] = x;
+    }
+    out[i] = tt_from_float<TOut>(x);
+}
+
+extern "C" int tt_add_narrow(float* residual, const float* delta, int splits, long long split_stride, void* out, int out_dtype,
+                             long long total, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (!delta) splits = 0;
+    if (out_dtype == TT_F32)
+        tt_launch_pdl(add_narrow_kernel<float>, dim3(blocks), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, (float*)out, (size_t)total);
+    else
+        tt_launch_pdl(add_narrow_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, residual, delta, splits, (size_t)split_stride, (__nv_bfloat16*)out, (size_t)total);
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// A gate times a slice of a second embedding of the token: out[t][j] = gelu_tanh(sum over slices of x[s][t][j]) *
+// table[tokens[t]][col_off + j], j < dim; the table has `table_cols` numbers a row.  A token outside the table raises the
+// status word's bad-token bit and gets zeros.
+// ------------------------------------------------------------------------------------
+template <typename TOut, typename TW>
+__global__ void token_side_gate_kernel(const float* __restrict__ x, int splits, size_t split_stride, const TW* __restrict__ table,
+                                       int vocab, int table_cols, int col_off, const int* __restrict__ tokens, int dim,
+                                       TOut* __restrict__ out, size_t total, unsigned* status) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / dim;
+    const int j = (int)(i - t * dim);
+    const int id = tokens[t];
+    if (id < 0 || id >= vocab) {
+        atomicOr(status, TT_STATUS_BAD_TOKEN);
+        out[i] = tt_from_float<TOut>(0.0f);
+        return;
+    }
+    float z = 0.0f;
+    for (int s = 0; s < splits; ++s) z += __ldg(x + s * split_stride + i);
+    out[i] = tt_from_float<TOut>(tt_gate_activation(z, 2) * tt_to_float(table[(size_t)id * table_cols + col_off + j]));
+}
+
+extern "C" int tt_token_side_gate(const float* x, int splits, long long split_stride, const void* table, int table_dtype, int vocab,
+                                  int table_cols, int col_off, const int* tokens, int n_tokens, int dim, void* out, int out_dtype,
+                                  unsigned* status, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * dim;
+    if (total == 0) return 0;
+    if (col_off < 0 || col_off + dim > table_cols) return (int)cudaErrorInvalidValue;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+#define TT_SIDE(TO, TW) tt_launch_pdl(token_side_gate_kernel<TO, TW>, dim3(blocks), dim3(threads), 0, stream, x, splits, (size_t)split_stride, (const TW*)table, vocab, table_cols, col_off, tokens, dim, (TO*)out, total, status)
+    if (out_dtype == TT_F32 && table_dtype == TT_F32) TT_SIDE(float, float);
+    else if (out_dtype == TT_F32) TT_SIDE(float, __nv_bfloat16);
+    else if (table_dtype == TT_F32) TT_SIDE(__nv_bfloat16, float);
+    else TT_SIDE(__nv_bfloat16, __nv_bfloat16);
+#undef TT_SIDE
+    TT_LAUNCH_CHECK();
+}
+
+// ------------------------------------------------------------------------------------
+// A sigmoid gate on a mixer's read-out, in place: y[t][c] *= sigmoid(sum over slices of gate[s][t][...]) with one gate
+// number per output number (column c) or per head (column c / head_width).  gate stands at the gate's first column; its
+// rows are gate_row numbers apart.
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ y, int cols, const float* __restrict__ gate, int splits, size_t split_stride,
+                                    int gate_row, int head_width, size_t total) {
+    tt_pdl_launch_dependents();
+    tt_pdl_wait();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const size_t t = i / cols;
+    const int c = (int)(i - t * cols);
+    const float* g = gate + t * (size_t)gate_row + (head_width > 0 ? c / head_width : c);
+    float z = 0.0f;
+    for (int s = 0; s < splits; ++s) z += __ldg(g + s * split_stride);
+    y[i] = tt_from_float<T>(tt_to_float(y[i]) / (1.0f + expf(-z)));
+}
+
+extern "C" int tt_sigmoid_gate(void* y, int dtype, int n_tokens, int cols, const float* gate, int splits, long long split_stride,
+                               int gate_row, int head_width, cudaStream_t stream) {
+    const size_t total = (size_t)n_tokens * cols;
+    if (total == 0) return 0;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((total + threads - 1) / threads);
+    if (dtype == TT_F32)
+        tt_launch_pdl(sigmoid_gate_kernel<float>, dim3(blocks), dim3(threads), 0, stream, (float*)y, cols, gate, splits, (size_t)split_stride, gate_row, head_width, total);
+    else
+        tt_launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)y, cols, gate, splits, (size_t)split_stride, gate_row, head_width, total);
     TT_LAUNCH_CHECK();
 }

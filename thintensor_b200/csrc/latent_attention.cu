@@ -6,13 +6,16 @@
 //
 // tt_latent_prepare: one block per token.  Sums the k-slices of the down projection [q latent | kv latent | k_rot],
 // divides the two latents by their root mean square (times their weights), writes the query latent for the
-// up projection, rotates k_rot by the token's position and appends [c | k_rot] to the token's cache row.
+// up projection, rotates k_rot by the token's position and appends [c | k_rot] to the token's cache row.  A layer whose
+// queries are projected directly has no query latent (q_rank 0); a token's row of the projection may hold more columns
+// behind these (row_stride).  The rotation pairs halves or, interleaved, neighbours; rot_scale multiplies cosine and sine.
 //
 // tt_latent_attention: three kernels.  (1) A block per (token, head) sums the slices of the head's query, rotates its
 // rotated part and forms a_h, threads across the latent.  (2) A warp per (token, head) and slice of the keys: a lane per
 // key of a tile of 32 (16-byte loads along the row), online softmax, the weighted latents accumulated with every lane
 // taking 16 bytes of a latent at a time; the slice leaves (sum, maximum, denominator) in scratch memory.  (3) A block per
-// (token, head) combines the slices in order and applies Wv_h, a warp per output number.
+// (token, head) combines the slices in order and applies Wv_h, a warp per output number, and multiplies the head by the
+// sigmoid of its gate number where the layer has one.
 //
 // Prompts may instead EXPAND the latents they can see into per-head keys and values for the step, laid out like blocks
 // of the ordinary cache (keys [block][head][64][dim + rot], values transposed [block][head][vdim][64]) with a table of
@@ -29,10 +32,26 @@ constexpr int LAT_MAX_RANK = 512;       // numbers of the latent (a lane accumul
 constexpr int LAT_MAX_ROW = 1024;       // rank + rot
 constexpr int LAT_MAX_DIM = 256;        // unrotated numbers of a head's query
 
+// Number j of a rotated part `part` (rotary_dim numbers rotate, the rest pass): its pair is j + half / j - half, or with
+// `interleaved` its neighbour j ^ 1 (pair index j / 2); cosine and sine are multiplied by rot_scale.
+__device__ __forceinline__ float lat_rotate(const float* __restrict__ part, int j, int rotary_dim, int interleaved, int pos,
+                                            const float* __restrict__ inv_freq, float rot_scale) {
+    if (j >= rotary_dim) return part[j];
+    const int half = rotary_dim >> 1;
+    const bool first = interleaved ? !(j & 1) : j < half;
+    const int pair = interleaved ? (j ^ 1) : (first ? j + half : j - half);
+    const int i = interleaved ? (j >> 1) : (first ? j : j - half);
+    float sn, cs;
+    sincosf((float)pos * __ldg(inv_freq + i), &sn, &cs);
+    sn *= rot_scale; cs *= rot_scale;
+    return first ? part[j] * cs - part[pair] * sn : part[j] * cs + part[pair] * sn;
+}
+
 template <typename TOut, typename TC>
-__global__ void latent_prepare_kernel(const float* __restrict__ down, int splits, size_t split_stride, int q_rank, int rank, int rot,
-                                      const float* __restrict__ q_weight, const float* __restrict__ kv_weight, float eps,
-                                      const float* __restrict__ inv_freq, int rotary_dim, TOut* __restrict__ q_latent,
+__global__ void latent_prepare_kernel(const float* __restrict__ down, int splits, size_t split_stride, int row_stride, int q_rank, int rank,
+                                      int rot, const float* __restrict__ q_weight, const float* __restrict__ kv_weight, float eps,
+                                      const float* __restrict__ inv_freq, int rotary_dim, int interleaved, float rot_scale,
+                                      TOut* __restrict__ q_latent,
                                       TC* __restrict__ pool, const int* __restrict__ table, int table_width, int pool_blocks,
                                       const int* __restrict__ cu, const int* __restrict__ len_before, int sequences,
                                       unsigned* status) {
@@ -44,7 +63,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, int splits
     extern __shared__ float lat_row[];                          // q_rank + rank + rot numbers, then 32 for the reductions
     const int cols = q_rank + rank + rot;
     float* reduce = lat_row + cols;
-    const float* src = down + (size_t)t * cols;
+    const float* src = down + (size_t)t * row_stride;
     float sq_q = 0.0f, sq_c = 0.0f;
     for (int j = threadIdx.x; j < cols; j += blockDim.x) {
         float x = 0.0f;
@@ -53,7 +72,7 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, int splits
         if (j < q_rank) sq_q = fmaf(x, x, sq_q);
         else if (j < q_rank + rank) sq_c = fmaf(x, x, sq_c);
     }
-    const float r_q = rsqrtf(tt_block_sum(sq_q, reduce) / (float)q_rank + eps);
+    const float r_q = q_rank > 0 ? rsqrtf(tt_block_sum(sq_q, reduce) / (float)q_rank + eps) : 0.0f;
     const float r_c = rsqrtf(tt_block_sum(sq_c, reduce) / (float)rank + eps);
     for (int j = threadIdx.x; j < q_rank; j += blockDim.x)
         q_latent[(size_t)t * q_rank + j] = tt_from_float<TOut>(lat_row[j] * r_q * __ldg(q_weight + j));
@@ -64,17 +83,8 @@ __global__ void latent_prepare_kernel(const float* __restrict__ down, int splits
     const float* c = lat_row + q_rank;
     for (int j = threadIdx.x; j < rank; j += blockDim.x) row[j] = tt_from_float<TC>(c[j] * r_c * __ldg(kv_weight + j));
     const float* kr = c + rank;
-    const int half = rotary_dim >> 1;
-    for (int j = threadIdx.x; j < rot; j += blockDim.x) {
-        float v = kr[j];
-        if (j < rotary_dim) {
-            const int i = j < half ? j : j - half;
-            float sn, cs;
-            sincosf((float)pos * __ldg(inv_freq + i), &sn, &cs);
-            v = j < half ? kr[j] * cs - kr[j + half] * sn : kr[j] * cs + kr[j - half] * sn;
-        }
-        row[rank + j] = tt_from_float<TC>(v);
-    }
+    for (int j = threadIdx.x; j < rot; j += blockDim.x)
+        row[rank + j] = tt_from_float<TC>(lat_rotate(kr, j, rotary_dim, interleaved, pos, inv_freq, rot_scale));
 }
 
 template <typename T> __device__ __forceinline__ float lat_weight(const T* p) { return tt_to_float(*p); }
@@ -104,10 +114,10 @@ template <> struct LatVec<__nv_bfloat16> {
 // The query a head's scores are taken with, one block per (token, head): [Wk_h^T q_plain | rotated q_rot] * scale, float32
 // [tokens][heads][rank + rot].  Threads run across the latent, so that a row of Wk_h is read side by side.
 template <typename TW>
-__global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, size_t q_stride, const TW* __restrict__ w_key,
+__global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, size_t q_stride, int q_row, const TW* __restrict__ w_key,
                                      const int* __restrict__ cu, const int* __restrict__ len_before, int sequences, int heads, int dim,
-                                     int rot, int rank, const float* __restrict__ inv_freq, int rotary_dim, float scale,
-                                     float* __restrict__ absorbed) {
+                                     int rot, int rank, const float* __restrict__ inv_freq, int rotary_dim, int interleaved,
+                                     float rot_scale, float scale, float* __restrict__ absorbed) {
     tt_pdl_launch_dependents();
     const int t = blockIdx.x / heads, h = blockIdx.x - t * heads;
     int pos = 0;
@@ -117,7 +127,7 @@ __global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, 
     }
     tt_pdl_wait();
     extern __shared__ float lat_shared[];                       // dim + rot
-    const float* qsrc = q + ((size_t)t * heads + h) * (dim + rot);
+    const float* qsrc = q + (size_t)t * q_row + (size_t)h * (dim + rot);
     for (int d = threadIdx.x; d < dim + rot; d += blockDim.x) {
         float x = 0.0f;
         for (int s = 0; s < q_splits; ++s) x += qsrc[(size_t)s * q_stride + d];
@@ -126,16 +136,8 @@ __global__ void latent_absorb_kernel(const float* __restrict__ q, int q_splits, 
     __syncthreads();
     float* out = absorbed + ((size_t)t * heads + h) * (rank + rot);
     const float* qr = lat_shared + dim;
-    const int half = rotary_dim >> 1;
-    for (int i = threadIdx.x; i < rot; i += blockDim.x) {
-        float v = qr[i];
-        if (i < rotary_dim) {
-            float sn, cs;
-            sincosf((float)pos * __ldg(inv_freq + (i < half ? i : i - half)), &sn, &cs);
-            v = i < half ? qr[i] * cs - qr[i + half] * sn : qr[i] * cs + qr[i - half] * sn;
-        }
-        out[rank + i] = v * scale;
-    }
+    for (int i = threadIdx.x; i < rot; i += blockDim.x)
+        out[rank + i] = lat_rotate(qr, i, rotary_dim, interleaved, pos, inv_freq, rot_scale) * scale;
     for (int r = threadIdx.x; r < rank; r += blockDim.x) {
         const TW* col = w_key + (size_t)h * dim * rank + r;
         float a[8];
@@ -523,12 +525,19 @@ latent_decode_mma_kernel(const float* __restrict__ absorbed, const __nv_bfloat16
 // output number takes Wv_h's row times it, lanes across the latent.
 template <typename TOut, typename TW>
 __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, const float* __restrict__ part_ml, int splits, int rank,
-                                           int vdim, int heads, const TW* __restrict__ w_value, TOut* __restrict__ out) {
+                                           int vdim, int heads, const TW* __restrict__ w_value, TOut* __restrict__ out,
+                                           const float* __restrict__ gate, int gate_splits, size_t gate_stride, int gate_row) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     extern __shared__ float lat_shared[];                       // rank, then splits
     const size_t row = blockIdx.x;
     const int h = (int)(row % heads);
+    float head_gate = 1.0f;                                     // sigmoid of the head's gate number, where the layer has one
+    if (gate) {
+        float z = 0.0f;
+        for (int s = 0; s < gate_splits; ++s) z += __ldg(gate + s * gate_stride + (row / heads) * (size_t)gate_row + h);
+        head_gate = 1.0f / (1.0f + expf(-z));
+    }
     const float* ml = part_ml + row * splits * 2;
     float m = -INFINITY;
     for (int s = 0; s < splits; ++s) m = fmaxf(m, ml[2 * s]);
@@ -566,7 +575,7 @@ __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, c
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
                 const float total = tt_warp_sum(o[i]);
-                if (lane == 0 && v0 + i < vdim) out[row * vdim + v0 + i] = tt_from_float<TOut>(total);
+                if (lane == 0 && v0 + i < vdim) out[row * vdim + v0 + i] = tt_from_float<TOut>(total * head_gate);
             }
         }
         return;
@@ -576,46 +585,48 @@ __global__ void latent_merge_expand_kernel(const float* __restrict__ part_acc, c
         float o = 0.0f;
         for (int r = lane; r < rank; r += 32) o = fmaf(lat_weight(wrow + r), lat_shared[r], o);
         o = tt_warp_sum(o);
-        if (lane == 0) out[row * vdim + v] = tt_from_float<TOut>(o);
+        if (lane == 0) out[row * vdim + v] = tt_from_float<TOut>(o * head_gate);
     }
 }
 
-extern "C" int tt_latent_prepare(const float* down, int splits, long long split_stride, int q_rank, int rank, int rot,
+extern "C" int tt_latent_prepare(const float* down, int splits, long long split_stride, int row_stride, int q_rank, int rank, int rot,
                                  const float* q_weight, const float* kv_weight, float eps, const float* inv_freq, int rotary_dim,
-                                 void* q_latent, int act_dtype, void* pool, int cache_dtype, const int* table, int table_width,
+                                 int interleaved, float rot_scale, void* q_latent, int act_dtype, void* pool, int cache_dtype, const int* table, int table_width,
                                  int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens, unsigned* status,
                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
-    if (rank <= 0 || q_rank <= 0 || rot < 0 || rotary_dim < 0 || rotary_dim > rot || (rotary_dim & 1) || act_dtype != cache_dtype)
-        return (int)cudaErrorInvalidValue;
     const int cols = q_rank + rank + rot;
+    if (rank <= 0 || q_rank < 0 || rot < 0 || rotary_dim < 0 || rotary_dim > rot || (rotary_dim & 1) || act_dtype != cache_dtype ||
+        row_stride < cols)
+        return (int)cudaErrorInvalidValue;
     const size_t shared = (size_t)(cols + 32) * sizeof(float);
     if (shared > 48 * 1024) return (int)cudaErrorInvalidValue;
     const int threads = cols >= 1024 ? 256 : 128;
-#define TT_PREP(T) tt_launch_pdl(latent_prepare_kernel<T, T>, dim3(n_tokens), dim3(threads), shared, stream, down, splits, (size_t)split_stride, q_rank, rank, rot, q_weight, kv_weight, eps, inv_freq, rotary_dim, (T*)q_latent, (T*)pool, table, table_width, pool_blocks, cu, len_before, sequences, status)
+#define TT_PREP(T) tt_launch_pdl(latent_prepare_kernel<T, T>, dim3(n_tokens), dim3(threads), shared, stream, down, splits, (size_t)split_stride, row_stride, q_rank, rank, rot, q_weight, kv_weight, eps, inv_freq, rotary_dim, interleaved, rot_scale, (T*)q_latent, (T*)pool, table, table_width, pool_blocks, cu, len_before, sequences, status)
     if (act_dtype == TT_F32) TT_PREP(float); else TT_PREP(__nv_bfloat16);
 #undef TT_PREP
     TT_LAUNCH_CHECK();
 }
 
-extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_stride, const void* w_key, const void* w_value,
+extern "C" int tt_latent_attention(const float* q, int q_splits, long long q_stride, int q_row, const void* w_key, const void* w_value,
                                    int weight_dtype, const void* pool, int act_dtype, const int* table, int table_width, int pool_blocks,
                                    const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int dim, int rot,
-                                   int vdim, int rank, const float* inv_freq, int rotary_dim, float scale, int window, int splits,
-                                   void* out, float* absorbed, float* part_acc, float* part_ml, int one_token_each, unsigned* status,
-                                   cudaStream_t stream) {
+                                   int vdim, int rank, const float* inv_freq, int rotary_dim, int interleaved, float rot_scale, float scale,
+                                   int window, int splits, void* out, float* absorbed, float* part_acc, float* part_ml,
+                                   int one_token_each, const float* gate, int gate_splits, long long gate_stride, int gate_row,
+                                   unsigned* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rank <= 0 || rank > LAT_MAX_RANK || rank + rot > LAT_MAX_ROW || dim <= 0 || dim > LAT_MAX_DIM || vdim <= 0 || splits < 1 ||
-        splits > 65535 || rotary_dim > rot || (rotary_dim & 1) || !absorbed || !part_acc || !part_ml)
+        splits > 65535 || rotary_dim > rot || (rotary_dim & 1) || !absorbed || !part_acc || !part_ml || q_row < heads * (dim + rot))
         return (int)cudaErrorInvalidValue;
     const long long rows = (long long)n_tokens * heads;
     const long long blocks = (rows + LAT_WARPS - 1) / LAT_WARPS;
     if (rows > 2147483647LL) return (int)cudaErrorInvalidValue;
     const size_t shared = (size_t)LAT_WARPS * (rank + rot) * sizeof(float);
     const dim3 grid((unsigned)blocks, splits), block(LAT_WARPS * 32);
-#define TT_ABSORB(TW) tt_launch_pdl(latent_absorb_kernel<TW>, dim3((unsigned)rows), dim3(rank >= 512 ? 512 : rank >= 256 ? 256 : 128), (size_t)(dim + rot) * sizeof(float), stream, q, q_splits, (size_t)q_stride, (const TW*)w_key, cu, len_before, sequences, heads, dim, rot, rank, inv_freq, rotary_dim, scale, absorbed)
+#define TT_ABSORB(TW) tt_launch_pdl(latent_absorb_kernel<TW>, dim3((unsigned)rows), dim3(rank >= 512 ? 512 : rank >= 256 ? 256 : 128), (size_t)(dim + rot) * sizeof(float), stream, q, q_splits, (size_t)q_stride, q_row, (const TW*)w_key, cu, len_before, sequences, heads, dim, rot, rank, inv_freq, rotary_dim, interleaved, rot_scale, scale, absorbed)
 #define TT_ATT(TA) tt_launch_pdl(latent_attention_kernel<TA>, grid, block, shared, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
-#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_expand_kernel<TA, TW>, dim3((unsigned)rows), dim3(256), (size_t)(rank + splits) * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, (const TW*)w_value, (TA*)out)
+#define TT_MERGE(TA, TW) tt_launch_pdl(latent_merge_expand_kernel<TA, TW>, dim3((unsigned)rows), dim3(256), (size_t)(rank + splits) * sizeof(float), stream, (const float*)part_acc, (const float*)part_ml, splits, rank, vdim, heads, (const TW*)w_value, (TA*)out, gate, gate_splits, (size_t)gate_stride, gate_row)
     if (weight_dtype == TT_F32) TT_ABSORB(float); else TT_ABSORB(__nv_bfloat16);
 #define TT_ATT_ROWS(TA) tt_launch_pdl(latent_attention_rows_kernel<TA>, grid, block, 0, stream, (const float*)absorbed, (const TA*)pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, rot, rank, window, splits, part_acc, part_ml, status)
     const int piece = act_dtype == TT_F32 ? 4 : 8;              // numbers in 16 bytes of a cache row
@@ -739,10 +750,12 @@ __global__ void latent_scatter_kernel(const float* __restrict__ y, int splits, s
 }
 
 // q: float32 partial sums [splits][tokens][heads * (dim + rot)]; out: the same numbers in T with each head's last rot
-// numbers rotated by the token's position (the first rotary_dim of them, halves paired).
+// numbers rotated by the token's position (the first rotary_dim of them, halves or neighbours paired); a token's row of q
+// is q_row numbers long.
 template <typename T>
-__global__ void latent_queries_kernel(const float* __restrict__ q, int splits, size_t split_stride, int heads, int dim, int rot,
-                                      const float* __restrict__ inv_freq, int rotary_dim, const int* __restrict__ cu,
+__global__ void latent_queries_kernel(const float* __restrict__ q, int splits, size_t split_stride, int q_row, int heads, int dim, int rot,
+                                      const float* __restrict__ inv_freq, int rotary_dim, int interleaved, float rot_scale,
+                                      const int* __restrict__ cu,
                                       const int* __restrict__ len_before, int sequences, T* __restrict__ out) {
     tt_pdl_launch_dependents();
     const int t = blockIdx.x;
@@ -750,18 +763,20 @@ __global__ void latent_queries_kernel(const float* __restrict__ q, int splits, s
     const int pos = len_before[b] + (t - cu[b]);
     tt_pdl_wait();
     const int hd = dim + rot, half = rotary_dim >> 1;
-    const float* row = q + (size_t)t * heads * hd;
+    const float* row = q + (size_t)t * q_row;
     for (int e = threadIdx.x; e < heads * hd; e += blockDim.x) {
         const int i = e % hd - dim;                             // index inside the rotated part, negative in front of it
         float x = 0.0f;
         for (int s = 0; s < splits; ++s) x += row[(size_t)s * split_stride + e];
         if (i >= 0 && i < rotary_dim) {
-            const int pair = i < half ? e + half : e - half;
+            const bool first = interleaved ? !(i & 1) : i < half;
+            const int pair = interleaved ? (first ? e + 1 : e - 1) : (first ? e + half : e - half);
             float other = 0.0f;
             for (int s = 0; s < splits; ++s) other += row[(size_t)s * split_stride + pair];
             float sn, cs;
-            sincosf((float)pos * __ldg(inv_freq + (i < half ? i : i - half)), &sn, &cs);
-            x = i < half ? x * cs - other * sn : x * cs + other * sn;
+            sincosf((float)pos * __ldg(inv_freq + (interleaved ? (i >> 1) : (first ? i : i - half))), &sn, &cs);
+            sn *= rot_scale; cs *= rot_scale;
+            x = first ? x * cs - other * sn : x * cs + other * sn;
         }
         out[(size_t)t * heads * hd + e] = tt_from_float<T>(x);
     }
@@ -800,15 +815,15 @@ extern "C" int tt_latent_scatter(const float* y, int splits, long long split_str
     TT_LAUNCH_CHECK();
 }
 
-extern "C" int tt_latent_queries(const float* q, int splits, long long split_stride, int heads, int dim, int rot, const float* inv_freq,
-                                 int rotary_dim, const int* cu, const int* len_before, int sequences, int n_tokens, void* out, int dtype,
+extern "C" int tt_latent_queries(const float* q, int splits, long long split_stride, int q_row, int heads, int dim, int rot,
+                                 const float* inv_freq, int rotary_dim, int interleaved, float rot_scale, const int* cu, const int* len_before, int sequences, int n_tokens, void* out, int dtype,
                                  cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (rotary_dim > rot || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     if (dtype == TT_F32)
-        tt_launch_pdl(latent_queries_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, heads, dim, rot, inv_freq, rotary_dim, cu, len_before, sequences, (float*)out);
+        tt_launch_pdl(latent_queries_kernel<float>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, q_row, heads, dim, rot, inv_freq, rotary_dim, interleaved, rot_scale, cu, len_before, sequences, (float*)out);
     else
-        tt_launch_pdl(latent_queries_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, heads, dim, rot, inv_freq, rotary_dim, cu, len_before, sequences, (__nv_bfloat16*)out);
+        tt_launch_pdl(latent_queries_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(256), 0, stream, q, splits, (size_t)split_stride, q_row, heads, dim, rot, inv_freq, rotary_dim, interleaved, rot_scale, cu, len_before, sequences, (__nv_bfloat16*)out);
     TT_LAUNCH_CHECK();
 }
 

@@ -319,7 +319,7 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
     normalised without a weight.  ``q_gain`` = (coef, every): queries at position p are multiplied by
     ``1 + coef * ln(floor((p + 1) / every) + 1)``.  ``value_from_keys``: the projection has no v heads; a value head is its
     key head before the norm."""
-    _need(proj, torch.float32, "projection")
+    proj_ptr, proj_splits, proj_stride, proj_row, _ = _projection_view(proj)     # may be the leading columns of a wider projection
     _need(inv_freq, torch.float32, "inv_freq")
     write = k_pool is not None
     if value_from_keys and value_dim != head_dim:
@@ -349,7 +349,7 @@ def qk_norm_rope_append(proj: torch.Tensor, q_norm: torch.Tensor | None, k_norm:
                                                        c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
                                                        c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_float, c_int,
                                                        c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(proj), proj.shape[0], proj.stride(0), cols, _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(inv_freq), rotary_dim,
+    _check(fn(proj_ptr, proj_splits, proj_stride, proj_row, _ptr(q_norm), _ptr(k_norm), norm_eps, _ptr(inv_freq), rotary_dim,
               1 if interleaved else 0, attention_scaling, _ptr(q_out), _ptr(k_pool), _ptr(v_pool), dtype_code(q_out.dtype), _ptr(table),
               table.shape[1], k_pool.shape[0] if write else 0, _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim,
               value_dim, 1 if write else 0, _ptr(cos_sin), _ptr(where), 1 if unit_norm else 0, 0.0 if q_gain is None else float(q_gain[0]),
@@ -408,7 +408,7 @@ def swiglu(gate_up: torch.Tensor, act: torch.Tensor, activation: str = "silu") -
               GATE_ACTIVATIONS[activation], _stream()), "swiglu")
 
 
-UNARY_ACTIVATIONS = {**GATE_ACTIVATIONS, "xielu": 3}
+UNARY_ACTIVATIONS = {**GATE_ACTIVATIONS, "xielu": 3, "gelu": 4}      # gelu: the exact one, with erf
 
 
 def activation(x: torch.Tensor, act: torch.Tensor, activation: str = "gelu_tanh", a: float = 0.0, c: float = 0.0) -> None:
@@ -456,10 +456,15 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
               len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
               scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
               part_ml: torch.Tensor | None, status: torch.Tensor, value_dim: int | None = None,
-              sinks: torch.Tensor | None = None) -> None:
+              sinks: torch.Tensor | None = None, softcap: float = 0.0, slopes: torch.Tensor | None = None,
+              gate: torch.Tensor | None = None, gate_per_head: bool = False) -> None:
     """Exact causal attention of ``n_tokens`` packed query tokens over the block cache.  ``value_dim``: the size of a
     value head where it differs from the keys'.  ``sinks`` (float32, one per query head): a term exp(sink) in the
-    softmax denominator that has no key and no value and is not scaled."""
+    softmax denominator that has no key and no value and is not scaled.  ``softcap`` > 0: a scaled score s becomes
+    ``softcap * tanh(s / softcap)``.  ``slopes`` (float32, one per query head): ``slope_h * (i - j)`` is taken off the score of
+    query position i and key position j.  ``gate``: float32 partial sums ``[slices, tokens, heads * value_dim]`` (with
+    ``gate_per_head``: ``[slices, tokens, heads]``), possibly a range of a wider projection's columns; the output is
+    multiplied by their sigmoid."""
     check_head_dim(head_dim)
     value_dim = head_dim if value_dim is None else int(value_dim)
     check_head_dim(value_dim)
@@ -468,11 +473,22 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table
         raise KernelError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
     if not (q.dtype == k_pool.dtype == v_pool.dtype == out.dtype):
         raise KernelError("queries, cache and output must share a dtype")
+    if slopes is not None:
+        _need(slopes, torch.float32, "slopes")
+        if slopes.numel() != heads:
+            raise KernelError(f"a slope per query head: {heads} numbers, got {slopes.numel()}")
+    g_ptr, g_splits, g_stride, g_row = c_void_p(0), 0, 0, 0
+    if gate is not None:
+        g_ptr, g_splits, g_stride, g_row, g_cols = _projection_view(gate)
+        if g_cols != (heads if gate_per_head else heads * value_dim) or gate.shape[1] != n_tokens:
+            raise KernelError("attention: the gate does not fit the heads")
     fn = _fn("attention", "tt_attention", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_float, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), dtype_code(q.dtype), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu),
               _ptr(len_before), sequences, n_tokens, heads, kv_heads, head_dim, value_dim, scale, _ptr(sinks), window, splits, _ptr(out),
-              _ptr(part_acc), _ptr(part_ml), _ptr(status), _stream()), "attention", 2 if splits > 1 else 1)
+              _ptr(part_acc), _ptr(part_ml), _ptr(status), float(softcap or 0.0), _ptr(slopes), g_ptr, g_splits, g_stride, g_row,
+              1 if gate_per_head else 0, _stream()), "attention", 2 if splits > 1 else 1)
 
 
 def differential_attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
@@ -683,6 +699,14 @@ def _projection(proj: torch.Tensor) -> tuple:
     return _ptr(proj), proj.shape[0], proj.stride(0), proj.shape[2]
 
 
+def _projection_view(proj: torch.Tensor) -> tuple:
+    """(pointer, splits, split stride, row stride, columns) of float32 partial sums [splits, tokens, cols] that may be a
+    range of the columns of a wider projection (``wide[:, :, a:b]``)."""
+    if proj.dtype != torch.float32 or proj.dim() != 3 or proj.stride(2) != 1:
+        raise KernelError("a projection's partial sums are float32 [splits, tokens, cols] with the columns side by side")
+    return _ptr(proj), proj.shape[0], proj.stride(0), proj.stride(1), proj.shape[2]
+
+
 def causal_conv(proj: torch.Tensor, col_off: int, channels: int, weight: torch.Tensor, bias: torch.Tensor | None, activation: bool,
                 state: torch.Tensor, out: torch.Tensor, cu: torch.Tensor, slots: torch.Tensor, sequences: int, n_tokens: int,
                 one_token_each: bool) -> None:
@@ -829,26 +853,36 @@ LATENT_MAX_RANK, LATENT_MAX_ROW, LATENT_MAX_DIM = 512, 1024, 256
 
 
 def latent_prepare(down: torch.Tensor, q_rank: int, rank: int, rot: int, q_weight: torch.Tensor, kv_weight: torch.Tensor, eps: float,
-                   inv_freq: torch.Tensor, rotary_dim: int, q_latent: torch.Tensor, pool: torch.Tensor | None, table: torch.Tensor,
-                   cu: torch.Tensor, len_before: torch.Tensor, sequences: int, n_tokens: int, status: torch.Tensor) -> None:
+                   inv_freq: torch.Tensor, rotary_dim: int, q_latent: torch.Tensor | None, pool: torch.Tensor | None, table: torch.Tensor,
+                   cu: torch.Tensor, len_before: torch.Tensor, sequences: int, n_tokens: int, status: torch.Tensor,
+                   interleaved: bool = False, rot_scale: float = 1.0) -> None:
     """From the partial sums of a down projection ``[q latent | kv latent | shared rotated key]``: both latents divided by
     their root mean square (``eps`` inside the root) times their weights; the query latent goes to ``q_latent`` ``[tokens,
     q_rank]``, and ``[kv latent | key part rotated by the position]`` to the token's row of ``pool`` ``[blocks, 1, 64, rank +
-    rot]`` (nothing is written without a pool)."""
-    for t, name in ((q_weight, "query latent norm"), (kv_weight, "latent norm"), (inv_freq, "inverse frequencies")):
+    rot]`` (nothing is written without a pool).  ``q_rank`` 0: no query latent (``q_weight`` and ``q_latent`` None).  ``down``
+    may be a range of a wider projection's columns.  ``interleaved``: the rotation pairs neighbours instead of halves;
+    ``rot_scale`` multiplies cosines and sines."""
+    for t, name in ((kv_weight, "latent norm"), (inv_freq, "inverse frequencies")):
         _need(t, torch.float32, name)
-    p, splits, stride, cols = _projection(down)
-    if cols != q_rank + rank + rot or tuple(q_latent.shape) != (n_tokens, q_rank) or not q_latent.is_contiguous():
+    p, splits, stride, row_stride, cols = _projection_view(down)
+    if q_rank:
+        _need(q_weight, torch.float32, "query latent norm")
+        if tuple(q_latent.shape) != (n_tokens, q_rank) or not q_latent.is_contiguous():
+            raise KernelError("latent_prepare: the query latent does not fit the sizes")
+    elif pool is None:
+        return                                          # nothing to norm and nothing to append
+    if cols != q_rank + rank + rot:
         raise KernelError("latent_prepare: shapes do not fit the sizes")
-    if pool is not None and (pool.dtype != q_latent.dtype or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot)):
+    if pool is not None and (tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot) or (q_rank and pool.dtype != q_latent.dtype)):
         raise KernelError("latent_prepare: the pool must be [blocks, 1, 64, rank + rot] in the activations' dtype")
     if (cols + 32) * 4 > 48 * 1024:
         raise KernelError(f"latent_prepare: {cols} projected numbers per token are more than the kernel stages")
-    fn = _fn("latent_attention", "tt_latent_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_void_p,
-                                                       c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p,
-                                                       c_int, c_int, c_void_p, c_void_p])
-    code = dtype_code(q_latent.dtype)
-    _check(fn(p, splits, stride, q_rank, rank, rot, _ptr(q_weight), _ptr(kv_weight), eps, _ptr(inv_freq), rotary_dim, _ptr(q_latent), code,
+    fn = _fn("latent_attention", "tt_latent_prepare", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_float,
+                                                       c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int,
+                                                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p])
+    code = dtype_code(q_latent.dtype if q_rank else pool.dtype)
+    _check(fn(p, splits, stride, row_stride, q_rank, rank, rot, _ptr(q_weight), _ptr(kv_weight), eps, _ptr(inv_freq), rotary_dim,
+              1 if interleaved else 0, float(rot_scale), _ptr(q_latent), code,
               _ptr(pool), code, _ptr(table), table.shape[1], 0 if pool is None else pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, _ptr(status), _stream()), "latent_prepare")
 
@@ -857,7 +891,8 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
                      len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, dim: int, rot: int, vdim: int, rank: int,
                      inv_freq: torch.Tensor, rotary_dim: int, scale: float, window: int, splits: int, out: torch.Tensor,
                      absorbed: torch.Tensor, part_acc: torch.Tensor, part_ml: torch.Tensor, status: torch.Tensor,
-                     tensor_cores: bool = False) -> None:
+                     tensor_cores: bool = False, interleaved: bool = False, rot_scale: float = 1.0,
+                     head_gate: torch.Tensor | None = None) -> None:
     """Causal softmax attention over a latent cache.  ``q``: float32 partial sums ``[slices, tokens, heads * (dim + rot)]`` of
     the queries (per head ``dim`` unrotated numbers, then ``rot`` of which the first ``rotary_dim`` are rotated here);
     ``w_key`` ``[heads * dim, rank]`` and ``w_value`` ``[heads * vdim, rank]`` expand a latent into a head's keys and values;
@@ -867,14 +902,22 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
     rot)]`` for the queries with ``w_key`` folded in; ``part_acc`` ``[tokens * heads * splits * rank]`` and ``part_ml``
     ``[tokens * heads * splits * 2]`` for the ``splits`` slices the keys are cut into.  ``tensor_cores``: a step of one token per
     sequence whose sizes :func:`latent_decode_tensor_cores` takes runs both products on the tensor cores, with the heads of a
-    token as the rows; ``splits`` must then cover every key a token can see in slices of ``LATENT_DECODE_SLICE`` keys."""
+    token as the rows; ``splits`` must then cover every key a token can see in slices of ``LATENT_DECODE_SLICE`` keys.
+    ``q`` may be a range of a wider projection's columns.  ``interleaved`` / ``rot_scale``: as in :func:`latent_prepare`.
+    ``head_gate``: float32 partial sums ``[slices, tokens, heads]`` (possibly such a range); every head's output is multiplied
+    by the sigmoid of its number."""
     if tensor_cores and (n_tokens != sequences or not latent_decode_tensor_cores(out.dtype, rank, rot)):
         raise KernelError("latent_attention: the tensor-core form is for steps of one token per sequence and sizes it takes")
     _need(inv_freq, torch.float32, "inverse frequencies")
     if rank > LATENT_MAX_RANK or rank + rot > LATENT_MAX_ROW or dim > LATENT_MAX_DIM:
         raise KernelError(f"latent attention takes latents of up to {LATENT_MAX_RANK}, rows of up to {LATENT_MAX_ROW} and "
                           f"{LATENT_MAX_DIM} unrotated numbers per head; got {rank}, {rank + rot}, {dim}")
-    p, q_splits, q_stride, q_cols = _projection(q)
+    p, q_splits, q_stride, q_row, q_cols = _projection_view(q)
+    g_ptr, g_splits, g_stride, g_row = c_void_p(0), 0, 0, 0
+    if head_gate is not None:
+        g_ptr, g_splits, g_stride, g_row, g_cols = _projection_view(head_gate)
+        if g_cols != heads or head_gate.shape[1] != n_tokens:
+            raise KernelError("latent_attention: the gate has one number per head and token")
     if (q_cols != heads * (dim + rot) or tuple(w_key.shape) != (heads * dim, rank) or tuple(w_value.shape) != (heads * vdim, rank)
             or w_key.dtype != w_value.dtype or not w_key.is_contiguous() or not w_value.is_contiguous()
             or tuple(pool.shape[1:]) != (1, BLOCK_TOKENS, rank + rot) or pool.dtype != out.dtype
@@ -885,14 +928,14 @@ def latent_attention(q: torch.Tensor, w_key: torch.Tensor, w_value: torch.Tensor
     if (absorbed.numel() < n_tokens * heads * (rank + rot) or part_acc.numel() < n_tokens * heads * splits * rank
             or part_ml.numel() < n_tokens * heads * splits * 2):
         raise KernelError("latent_attention: scratch memory is too small")
-    fn = _fn("latent_attention", "tt_latent_attention", [c_void_p, c_int, c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
+    fn = _fn("latent_attention", "tt_latent_attention", [c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p,
                                                          c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                                         c_void_p, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                                                         c_int, c_void_p, c_void_p])
-    _check(fn(p, q_splits, q_stride, _ptr(w_key), _ptr(w_value), dtype_code(w_key.dtype), _ptr(pool), dtype_code(out.dtype), _ptr(table),
+                                                         c_void_p, c_int, c_int, c_float, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                                         c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_void_p, c_void_p])
+    _check(fn(p, q_splits, q_stride, q_row, _ptr(w_key), _ptr(w_value), dtype_code(w_key.dtype), _ptr(pool), dtype_code(out.dtype), _ptr(table),
               table.shape[1], pool.shape[0], _ptr(cu), _ptr(len_before), sequences, n_tokens, heads, dim, rot, vdim, rank, _ptr(inv_freq),
-              rotary_dim, scale, window, splits, _ptr(out), _ptr(absorbed), _ptr(part_acc), _ptr(part_ml), 2 if tensor_cores else 0, _ptr(status),
-              _stream()), "latent_attention", 3)
+              rotary_dim, 1 if interleaved else 0, float(rot_scale), scale, window, splits, _ptr(out), _ptr(absorbed), _ptr(part_acc),
+              _ptr(part_ml), 2 if tensor_cores else 0, g_ptr, g_splits, g_stride, g_row, _ptr(status), _stream()), "latent_attention", 3)
 
 
 LATENT_DECODE_SLICE = 64        # keys of one slice of the tensor-core decode form (LT_KEYS in csrc/latent_attention.cu)
@@ -951,31 +994,95 @@ def latent_scatter(y: torch.Tensor, heads: int, dim: int, rot: int, vdim: int, k
 
 
 def latent_queries(q: torch.Tensor, heads: int, dim: int, rot: int, inv_freq: torch.Tensor, rotary_dim: int, cu: torch.Tensor,
-                   len_before: torch.Tensor, sequences: int, n_tokens: int, out: torch.Tensor) -> None:
-    """The queries of the expanded form: the partial sums ``q`` ``[slices, tokens, heads * (dim + rot)]`` summed, every head's
-    last ``rot`` numbers rotated by the position (the first ``rotary_dim`` of them, halves paired), narrowed to ``out``."""
+                   len_before: torch.Tensor, sequences: int, n_tokens: int, out: torch.Tensor, interleaved: bool = False,
+                   rot_scale: float = 1.0) -> None:
+    """The queries of the expanded form: the partial sums ``q`` ``[slices, tokens, heads * (dim + rot)]`` (possibly a range of a
+    wider projection's columns) summed, every head's last ``rot`` numbers rotated by the position (the first ``rotary_dim`` of
+    them, halves or neighbours paired, cosines and sines times ``rot_scale``), narrowed to ``out``."""
     _need(inv_freq, torch.float32, "inverse frequencies")
-    p, splits, stride, cols = _projection(q)
+    p, splits, stride, q_row, cols = _projection_view(q)
     if cols != heads * (dim + rot) or tuple(out.shape) != (n_tokens, cols) or not out.is_contiguous():
         raise KernelError("latent_queries: shapes do not fit the sizes")
-    fn = _fn("latent_attention", "tt_latent_queries", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p,
-                                                       c_int, c_int, c_void_p, c_int, c_void_p])
-    _check(fn(p, splits, stride, heads, dim, rot, _ptr(inv_freq), rotary_dim, _ptr(cu), _ptr(len_before), sequences, n_tokens, _ptr(out),
-              dtype_code(out.dtype), _stream()), "latent_queries")
+    fn = _fn("latent_attention", "tt_latent_queries", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_float,
+                                                       c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p])
+    _check(fn(p, splits, stride, q_row, heads, dim, rot, _ptr(inv_freq), rotary_dim, 1 if interleaved else 0, float(rot_scale), _ptr(cu),
+              _ptr(len_before), sequences, n_tokens, _ptr(out), dtype_code(out.dtype), _stream()), "latent_queries")
+
+
+# ------------------------------------------------------------------ stream, side input, gates
+def add_narrow(residual: torch.Tensor, delta: torch.Tensor | None, out: torch.Tensor) -> None:
+    """residual += sum of the float32 slices ``delta`` [slices, tokens, hidden] (None: nothing to add); ``out`` = the stream
+    in the activation dtype, for a part that reads the stream itself."""
+    _need(residual, torch.float32, "residual")
+    if tuple(out.shape) != tuple(residual.shape) or not out.is_contiguous():
+        raise KernelError("add_narrow: the output has the stream's shape")
+    p, splits, stride = c_void_p(0), 0, 0
+    if delta is not None:
+        p, splits, stride, cols = _projection(delta)
+        if tuple(delta.shape[1:]) != tuple(residual.shape):
+            raise KernelError("add_narrow: the delta does not fit the stream")
+    fn = _fn("elementwise", "tt_add_narrow", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_void_p])
+    _check(fn(_ptr(residual), p, splits, stride, _ptr(out), dtype_code(out.dtype), residual.numel(), _stream()), "add_narrow")
+
+
+def token_side_gate(x: torch.Tensor, table: torch.Tensor, col_off: int, tokens: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+    """out[t, j] = gelu_tanh(sum of the float32 slices x[s, t, j]) * table[tokens[t], col_off + j] for j < dim."""
+    p, splits, stride, dim = _projection(x)
+    _need(tokens, torch.int32, "tokens")
+    n = tokens.numel()
+    if table.dim() != 2 or not table.is_contiguous() or x.shape[1] != n or tuple(out.shape) != (n, dim) or not out.is_contiguous():
+        raise KernelError("token_side_gate: shapes do not fit")
+    if col_off < 0 or col_off + dim > table.shape[1]:
+        raise KernelError("token_side_gate: the slice lies outside the table's rows")
+    fn = _fn("elementwise", "tt_token_side_gate", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int,
+                                                   c_void_p, c_int, c_void_p, c_void_p])
+    _check(fn(p, splits, stride, _ptr(table), dtype_code(table.dtype), table.shape[0], table.shape[1], col_off, _ptr(tokens), n, dim,
+              _ptr(out), dtype_code(out.dtype), _ptr(status), _stream()), "token_side_gate")
+
+
+def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor, head_width: int = 0) -> None:
+    """In place: y[t, c] *= sigmoid(sum of the float32 slices gate[s, t, c]), or with ``head_width`` > 0 one gate number per
+    head, gate[s, t, c // head_width].  ``gate`` may be a range of a wider projection's columns."""
+    g_ptr, g_splits, g_stride, g_row, g_cols = _projection_view(gate)
+    if y.dim() != 2 or not y.is_contiguous() or gate.shape[1] != y.shape[0]:
+        raise KernelError("sigmoid_gate: shapes do not fit")
+    if g_cols != (y.shape[1] // head_width if head_width > 0 else y.shape[1]):
+        raise KernelError("sigmoid_gate: the gate does not fit the columns")
+    fn = _fn("elementwise", "tt_sigmoid_gate", [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
+    _check(fn(_ptr(y), dtype_code(y.dtype), y.shape[0], y.shape[1], g_ptr, g_splits, g_stride, g_row, int(head_width), _stream()), "sigmoid_gate")
 
 
 # ------------------------------------------------------------------------------ routing
 ROUTE_MAX_EXPERTS = 512
 
 
+def _route_options(experts: int, score: str, correction: torch.Tensor | None, group_score: str, renormalize: bool, extra: int) -> tuple:
+    if score not in ("softmax", "sigmoid") or group_score not in ("max", "top2"):
+        raise KernelError("routing scores are 'softmax' or 'sigmoid', group scores 'max' or 'top2'")
+    if correction is not None:
+        _need(correction, torch.float32, "the choice correction")
+        if correction.numel() != experts:
+            raise KernelError(f"a correction per expert: {experts} numbers, got {correction.numel()}")
+    if not 0 <= extra <= 32:
+        raise KernelError("up to 32 always-on gates")
+    return (1 if score == "sigmoid" else 0, _ptr(correction), 1 if group_score == "top2" else 0, 0 if renormalize else 1, int(extra))
+
+
 def route_topk(logits: torch.Tensor, top: int, groups: int, keep: int, gates: torch.Tensor, chosen: torch.Tensor,
-               weights: torch.Tensor) -> None:
+               weights: torch.Tensor, score: str = "softmax", correction: torch.Tensor | None = None, group_score: str = "max",
+               renormalize: bool = True, extra: int = 0) -> None:
     """Routing of a mixture of experts from the router's logits (float32 partial sums ``[slices, tokens, experts]``): scores
     are the softmax over all experts; experts form ``groups`` equal groups of neighbours, a group's score is its largest
     expert score, and only experts of the ``keep`` best groups can be chosen; the ``top`` largest of those are chosen (ties:
     the lower index) and weighted by score / (sum of the chosen scores + 1e-20).  ``chosen`` int32 and ``weights`` float32
-    ``[tokens, top]``; ``gates`` float32 ``[tokens, experts]`` holds the same densely, zero for experts not chosen."""
+    ``[tokens, top]``; ``gates`` float32 ``[tokens, experts]`` holds the same densely, zero for experts not chosen.
+    ``score`` "sigmoid": scores are the logits' sigmoids.  ``correction`` (float32, one per expert) is added to the scores for
+    the choice only (groups and experts); weights stay the scores.  ``group_score`` "top2": a group's score is the sum of its
+    two largest choice scores.  ``renormalize`` off: the weights are the chosen scores themselves.  ``extra``: so many more
+    logits follow the experts'; ``gates`` then has ``experts + extra`` columns, the last ones the sigmoids of those logits."""
     p, splits, stride, experts = _projection(logits)
+    experts -= extra
+    options = _route_options(experts, score, correction, group_score, renormalize, extra)
     tokens = logits.shape[1]
     _need(gates, torch.float32, "gates")
     _need(weights, torch.float32, "routing weights")
@@ -984,36 +1091,39 @@ def route_topk(logits: torch.Tensor, top: int, groups: int, keep: int, gates: to
             or not 1 <= keep <= groups):
         raise KernelError(f"route_topk takes up to {ROUTE_MAX_EXPERTS} experts in up to 32 equal groups and up to 32 choices; got "
                           f"{experts} experts, {groups} groups of which {keep} stay, top {top}")
-    if tuple(gates.shape) != (tokens, experts) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
+    if tuple(gates.shape) != (tokens, experts + extra) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
         raise KernelError("route_topk: outputs do not fit the sizes")
     fn = _fn("routing", "tt_route_topk", [c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-                                          c_void_p])
-    _check(fn(p, splits, stride, tokens, experts, top, groups, keep, _ptr(gates), _ptr(chosen), _ptr(weights), _stream()), "route_topk")
+                                          c_int, c_void_p, c_int, c_int, c_int, c_void_p])
+    _check(fn(p, splits, stride, tokens, experts, top, groups, keep, _ptr(gates), _ptr(chosen), _ptr(weights), *options, _stream()),
+           "route_topk")
 
 
 def route_rows(x: torch.Tensor, w: torch.Tensor, top: int, groups: int, keep: int, gates: torch.Tensor, chosen: torch.Tensor,
-               weights: torch.Tensor) -> None:
+               weights: torch.Tensor, score: str = "softmax", correction: torch.Tensor | None = None, group_score: str = "max",
+               renormalize: bool = True, extra: int = 0) -> None:
     """:func:`route_topk` with the router's product ``x @ w.T`` (float32 sums) in front, in one kernel: ``x`` ``[tokens,
-    hidden]`` and ``w`` ``[experts, hidden]``, each float32 or bfloat16."""
+    hidden]`` and ``w`` ``[experts + extra, hidden]``, each float32 or bfloat16."""
     tokens, hidden = x.shape
-    experts = w.shape[0]
+    experts = w.shape[0] - extra
+    options = _route_options(experts, score, correction, group_score, renormalize, extra)
     _need(gates, torch.float32, "gates")
     _need(weights, torch.float32, "routing weights")
     _need(chosen, torch.int32, "chosen experts")
     if not x.is_contiguous() or not w.is_contiguous() or w.shape[1] != hidden:
         raise KernelError("route_rows: the rows and the router's matrix must be contiguous and of one width")
-    if not route_rows_takes(hidden, experts):
+    if not route_rows_takes(hidden, experts + extra):
         raise KernelError(f"route_rows stages a row of up to {ROUTE_MAX_HIDDEN} numbers, got {hidden}")
     if (experts > ROUTE_MAX_EXPERTS or not 1 <= top <= min(32, experts) or not 1 <= groups <= 32 or experts % groups
             or not 1 <= keep <= groups):
         raise KernelError(f"route_rows takes up to {ROUTE_MAX_EXPERTS} experts in up to 32 equal groups and up to 32 choices; got "
                           f"{experts} experts, {groups} groups of which {keep} stay, top {top}")
-    if tuple(gates.shape) != (tokens, experts) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
+    if tuple(gates.shape) != (tokens, experts + extra) or tuple(chosen.shape) != (tokens, top) or tuple(weights.shape) != (tokens, top):
         raise KernelError("route_rows: outputs do not fit the sizes")
     fn = _fn("routing", "tt_route_rows", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                          c_void_p, c_void_p])
+                                          c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(fn(_ptr(x), dtype_code(x.dtype), _ptr(w), dtype_code(w.dtype), hidden, tokens, experts, top, groups, keep, _ptr(gates),
-              _ptr(chosen), _ptr(weights), _stream()), "route_rows")
+              _ptr(chosen), _ptr(weights), *options, _stream()), "route_rows")
 
 
 ROUTE_MAX_HIDDEN = 11000
@@ -1033,6 +1143,27 @@ def scale_expert_columns(act: torch.Tensor, width: int, gates: torch.Tensor) -> 
         raise KernelError("scale_expert_columns: the activations do not fit the gates")
     fn = _fn("routing", "tt_scale_expert_columns", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
     _check(fn(_ptr(act), dtype_code(act.dtype), tokens, act.stride(0), width, experts, _ptr(gates), _stream()), "scale_expert_columns")
+
+
+def expert_activation(gate_up: torch.Tensor, act: torch.Tensor, experts: int, width: int, shared_width: int, limit: float,
+                      shared_limit: float, alpha: float, gates: torch.Tensor, shared_gated: bool) -> None:
+    """The clamped gated unit of a mixture's experts with the routing weights applied: ``gate_up`` float32 partial sums
+    ``[slices, tokens, 2 * cols]`` (gate columns first), ``cols = experts * width + shared_width``.  With ``g' = min(g, limit)``
+    and ``u' = clamp(u, -limit, limit)``: ``act[t, c] = g' sigmoid(alpha g') (u' + 1) * gates[t, c // width]`` for the routed
+    experts' columns; the always-on expert's columns behind them use ``shared_limit`` and ``gates[t, experts]`` (``shared_gated``)
+    or no weight.  A limit of 0 or less: no clamp."""
+    p, splits, stride, cols2 = _projection(gate_up)
+    _need(gates, torch.float32, "gates")
+    tokens = gate_up.shape[1]
+    cols = experts * width + shared_width
+    if cols2 != 2 * cols or tuple(act.shape) != (tokens, cols) or not act.is_contiguous() or gates.shape[0] != tokens:
+        raise KernelError("expert_activation: shapes do not fit the sizes")
+    if gates.shape[1] < experts + (1 if shared_gated else 0):
+        raise KernelError("expert_activation: too few gates a token")
+    fn = _fn("routing", "tt_expert_activation", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                                 c_float, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(p, splits, stride, _ptr(act), dtype_code(act.dtype), tokens, experts, width, shared_width, float(limit or 0.0),
+              float(shared_limit or 0.0), float(alpha), _ptr(gates), gates.shape[1], 1 if shared_gated else 0, _stream()), "expert_activation")
 
 
 # -------------------------------------------------------------------------------- gemm

@@ -1,2 +1,2 @@
 """Built-in architectures.  Importing this package registers them."""
-from . import famalorn, llama, neruzen, sogidra  # noqa: F401
+from . import famalorn, kerepel, llama, neruzen, sogidra  # noqa: F401

@@ -25,10 +25,11 @@ from .base import ARRANGEMENTS, Arrangement, Delta, DepthStep
 @ARRANGEMENTS.register("pre_norm")
 class PreNorm(Arrangement):
     """A layer without a feed-forward leaves out ``ffn_norm`` and ``ffn``: its mixer's output is then what the next
-    layer's norm adds."""
+    layer's norm adds.  ``side`` (optional): a side input at the layer's end, which reads the stream with the last
+    sublayer's output added and hands on what it adds itself."""
 
-    roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn"}
-    optional = ("ffn_norm", "ffn")
+    roles = {"mixer_norm": "norm", "mixer": "mixer", "ffn_norm": "norm", "ffn": "ffn", "side": "side"}
+    optional = ("ffn_norm", "ffn", "side")
 
     def __init__(self, parts):
         super().__init__(parts)
@@ -48,11 +49,13 @@ class PreNorm(Arrangement):
         ctx.residual = residual
         normed = ctx.scratch("block.normed", (ctx.n_tokens, hidden))
         self.parts["mixer_norm"].forward(ctx, residual, pending, normed)
-        mixed = self.parts["mixer"].forward(ctx, normed, caches[0], states[0])
-        if "ffn" not in self.parts:
-            return mixed
-        self.parts["ffn_norm"].forward(ctx, residual, mixed, normed)
-        return self.parts["ffn"].forward(ctx, normed)
+        last = self.parts["mixer"].forward(ctx, normed, caches[0], states[0])
+        if "ffn" in self.parts:
+            self.parts["ffn_norm"].forward(ctx, residual, last, normed)
+            last = self.parts["ffn"].forward(ctx, normed)
+        if "side" in self.parts:
+            last = self.parts["side"].forward(ctx, residual, last)
+        return last
 
 
 @ARRANGEMENTS.register("pre_norm_pair")

@@ -12,7 +12,14 @@ Options beyond that form, each a parameter: value heads of another size than key
 by a weight of ``head_dim`` numbers that all heads share, before the rotation
 (``qk_norm_eps``); a learned number per query head whose exponential joins the softmax
 denominator without a key or a value (``sink``); a rotation that pairs neighbouring numbers
-(the position encoding's ``interleaved``).  A layer that uses any of them runs the general
+(the position encoding's ``interleaved``); a short causal convolution over time on every channel
+of q, k and v right after their projections, ``y_t = sum_j w[:, j] u_(t - taps + 1 + j)`` with zeros before the
+sequence (``conv`` taps; the last ``taps - 1`` projected rows are a per-sequence state); scores capped by
+``softcap * tanh(s / softcap)``; a bias that grows with the distance, ``slope_h * (i - j)`` taken off the score with
+``slope_h = 2 ** (-slope_exponent * (h + 1) / heads)``; the concatenated heads multiplied by ``sigmoid(W_g x)`` before the
+output projection (``gate="elementwise"``, or ``"head"`` for one number per head); no key and value projections at
+all, for a run of the schedule that reads an earlier run's cache (``own_keys`` off); a cache that keeps more tokens than
+the layer's own window (``cache_window``, for the readers of its cache; -1: every token).  A layer that uses any of them runs the general
 kernels: one that normalises, rotates and appends, and the exact attention.
 """
 from __future__ import annotations
@@ -20,7 +27,7 @@ from __future__ import annotations
 import torch
 
 from ..kernels import api
-from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, RotaryTable, WeightDecl
+from .base import MIXERS, POSITION_ENCODINGS, Delta, KVNeed, Mixer, RotaryTable, StateNeed, WeightDecl
 from .linear import Linear
 from .spec import PartSpec
 
@@ -40,11 +47,14 @@ def kv_splits(ctx, parallel_units: int, keys_per_slice: int, target_units: int) 
 @MIXERS.register("attention")
 class CausalAttention(Mixer):
     NAMES = {"q": "q_proj.weight", "k": "k_proj.weight", "v": "v_proj.weight", "o": "o_proj.weight",
-             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks"}
+             "q_norm": "q_norm.weight", "k_norm": "k_norm.weight", "sink": "sinks", "g": "g_proj.weight",
+             "q_conv": "q_conv.weight", "k_conv": "k_conv.weight", "v_conv": "v_conv.weight"}
 
     def __init__(self, hidden: int, heads: int, kv_heads: int, head_dim: int, position: PartSpec | None = None,
                  bias: bool = False, window: int | None = None, scale: float | None = None, value_dim: int | None = None,
-                 qk_norm_eps: float | None = None, sink: bool = False, names: dict | None = None):
+                 qk_norm_eps: float | None = None, sink: bool = False, names: dict | None = None, conv: int | None = None,
+                 softcap: float | None = None, slope_exponent: float | None = None, gate: str | None = None, own_keys: bool = True,
+                 cache_window: int | None = None):
         self.hidden, self.heads, self.kv_heads, self.head_dim = int(hidden), int(heads), int(kv_heads), int(head_dim)
         if self.heads % self.kv_heads:
             raise ValueError(f"{heads} query heads are not a multiple of {kv_heads} key/value heads")
@@ -58,6 +68,18 @@ class CausalAttention(Mixer):
         self.k_norm: torch.Tensor | None = None
         self.sinks: torch.Tensor | None = None
         self.bias = bool(bias)
+        self.conv = int(conv) if conv else 0
+        if self.conv and not 1 <= self.conv <= 8:
+            raise ValueError("the convolution kernel takes 1 to 8 taps")
+        self.softcap = float(softcap) if softcap else 0.0
+        self.slope_exponent = None if slope_exponent is None else float(slope_exponent)
+        if gate not in (None, "elementwise", "head"):
+            raise ValueError(f"an output gate is 'elementwise' or 'head', not {gate!r}")
+        self.gate = gate
+        self.own_keys = bool(own_keys)
+        self.cache_window = None if not cache_window else int(cache_window)       # -1: the cache keeps every token
+        self.slopes: torch.Tensor | None = None
+        self.conv_weight: torch.Tensor | None = None
         self.window = None if not window else int(window)
         self.scale = float(scale) if scale is not None else self.head_dim ** -0.5
         position = position or PartSpec("none", {"head_dim": self.head_dim})
@@ -73,15 +95,22 @@ class CausalAttention(Mixer):
     def weights(self) -> dict[str, WeightDecl]:
         q, kv = self.heads * self.head_dim, self.kv_heads * self.head_dim
         n = self.names
-        out = {
-            n["q"]: WeightDecl((q, self.hidden)),
-            n["k"]: WeightDecl((kv, self.hidden)),
-            n["v"]: WeightDecl((self.kv_heads * self.value_dim, self.hidden)),
-            n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim)),
-        }
+        out = {n["q"]: WeightDecl((q, self.hidden))}
+        if self.own_keys:
+            out[n["k"]] = WeightDecl((kv, self.hidden))
+            out[n["v"]] = WeightDecl((self.kv_heads * self.value_dim, self.hidden))
+        out[n["o"]] = WeightDecl((self.hidden, self.heads * self.value_dim))
         if self.qk_norm_eps is not None:
             out[n["q_norm"]] = WeightDecl((self.head_dim,), init="norm")
-            out[n["k_norm"]] = WeightDecl((self.head_dim,), init="norm")
+            if self.own_keys:
+                out[n["k_norm"]] = WeightDecl((self.head_dim,), init="norm")
+        if self.conv:
+            out[n["q_conv"]] = WeightDecl((q, self.conv), init="small")
+            if self.own_keys:
+                out[n["k_conv"]] = WeightDecl((kv, self.conv), init="small")
+                out[n["v_conv"]] = WeightDecl((self.kv_heads * self.value_dim, self.conv), init="small")
+        if self.gate:
+            out[n["g"]] = WeightDecl((self.gate_cols, self.hidden))
         if self.sink:
             out[n["sink"]] = WeightDecl((self.heads,))
         if self.bias:
@@ -91,13 +120,29 @@ class CausalAttention(Mixer):
             })
         return out
 
+    @property
+    def gate_cols(self) -> int:
+        return 0 if not self.gate else (self.heads if self.gate == "head" else self.heads * self.value_dim)
+
+    @property
+    def conv_channels(self) -> int:
+        """What passes the convolution: q, and k and v where the layer projects them."""
+        return self.heads * self.head_dim + (self.kv_heads * (self.head_dim + self.value_dim) if self.own_keys else 0)
+
     def cache_need(self) -> KVNeed:
-        return KVNeed(self.kv_heads, self.head_dim, self.window, None if self.value_dim == self.head_dim else self.value_dim)
+        window = self.window
+        if window is not None and self.cache_window:
+            window = None if self.cache_window < 0 else max(window, self.cache_window)
+        return KVNeed(self.kv_heads, self.head_dim, window, None if self.value_dim == self.head_dim else self.value_dim)
+
+    def state_needs(self) -> list[StateNeed]:
+        return [StateNeed((self.conv - 1, self.conv_channels), torch.float32)] if self.conv > 1 else []
 
     @property
     def general(self) -> bool:
         """Whether the layer needs the general kernels (see the module's text)."""
-        return (self.value_dim != self.head_dim or self.qk_norm_eps is not None or self.sink
+        return (self.value_dim != self.head_dim or self.qk_norm_eps is not None or self.sink or bool(self.conv) or self.softcap > 0.0
+                or self.slope_exponent is not None or self.gate is not None or not self.own_keys
                 or (self.rot is not None and self.rot.interleaved and self.rot.rotary_dim > 0))
 
     def bind(self, tensors, dtype, device) -> None:
@@ -113,19 +158,29 @@ class CausalAttention(Mixer):
             raise ValueError("attention with a value size of its own, a query/key norm, a sink or an interleaved rotation takes no biases")
         if self.qk_norm_eps is not None:
             self.q_norm = tensors[n["q_norm"]].to(torch.float32).contiguous()
-            self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous()
+            self.k_norm = tensors[n["k_norm"]].to(torch.float32).contiguous() if self.own_keys else None
         if self.sink:
             self.sinks = tensors[n["sink"]].to(torch.float32).contiguous()
-        weight = torch.cat([tensors[n["q"]], tensors[n["k"]], tensors[n["v"]]], dim=0)
+        if self.slope_exponent is not None:     # float64 powers, rounded once
+            head = torch.arange(1, self.heads + 1, dtype=torch.float64)
+            self.slopes = torch.pow(2.0, -self.slope_exponent * head / self.heads).to(torch.float32).to(device)
+        inputs = ("q", "k", "v") if self.own_keys else ("q",)
+        if self.conv:
+            self.conv_weight = torch.cat([tensors[n[key + "_conv"]].to(torch.float32) for key in inputs], dim=0).contiguous()
+        rows = [tensors[n[key]] for key in inputs] + ([tensors[n["g"]]] if self.gate else [])
+        weight = torch.cat(rows, dim=0) if len(rows) > 1 else rows[0]
         bias = None
         if self.bias:
             bias = torch.cat([tensors["q_proj.bias"].float(), tensors["k_proj.bias"].float(), tensors["v_proj.bias"].float()])
-        self.qkv = Linear(weight, bias)
-        self.q_only = self.qkv.rows(0, self.heads * self.head_dim)
+        self.qkv = Linear(weight, bias)                # [q | k | v | gate], without k and v in a layer that reads another's cache
+        self.q_only = self.qkv.rows(0, self.heads * self.head_dim) if self.own_keys and not self.gate else self.qkv
         self.out = Linear(tensors[n["o"]], tensors["o_proj.bias"] if self.bias else None)
 
     def projections(self) -> list:
         return [self.qkv, self.out]             # q_only is a view of qkv's first rows
+
+    def vectors(self) -> list[torch.Tensor]:
+        return [t for t in (self.q_norm, self.k_norm, self.conv_weight, self.slopes) if t is not None]
 
     def device_driven(self) -> bool:
         return True
@@ -139,15 +194,25 @@ class CausalAttention(Mixer):
         rot = self.rot
         mixed = ctx.scratch("attention.mixed", (ctx.n_tokens, self.heads * self.value_dim))
         if self.general:
+            if cache.writes != self.own_keys and (self.gate or self.conv or not self.own_keys):
+                raise RuntimeError("an attention layer writes the cache exactly when it projects keys and values of its own")
             projection = (self.qkv if cache.writes else self.q_only)(ctx, x, "attention.qkv")
+            gate = projection[:, :, projection.shape[2] - self.gate_cols:] if self.gate else None
+            source = projection[:, :, :projection.shape[2] - self.gate_cols] if self.gate else projection
+            if self.conv:                          # q, k and v pass the convolution on their way from the product to the norm
+                mixed_in = ctx.scratch("attention.conv", (1, ctx.n_tokens, self.conv_channels), torch.float32)
+                tail = states[0] if self.conv > 1 else ctx.scratch("attention.no_tail", (1, 0, self.conv_channels), torch.float32)
+                api.causal_conv(projection, 0, self.conv_channels, self.conv_weight, None, False, tail, mixed_in[0], ctx.cu, ctx.slots,
+                                ctx.sequences, ctx.n_tokens, ctx.decode)
+                source = mixed_in
             q = ctx.scratch("attention.q", (ctx.n_tokens, q_cols))
             # prompts: positions, cosines and sines come from the step's table, made once for all layers and heads
             cos_sin, where = self.step_rope_table(ctx) if (rot.rotary_dim and not ctx.decode) else (None, None)
-            api.qk_norm_rope_append(projection, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq, rot.rotary_dim,
+            api.qk_norm_rope_append(source, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0, rot.inv_freq, rot.rotary_dim,
                                     rot.interleaved, rot.attention_scaling, q, cache.k_pool if cache.writes else None,
                                     cache.v_pool if cache.writes else None, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                                     self.heads, self.kv_heads, self.head_dim, self.value_dim, ctx.status, cos_sin, where)
-            self.attend(ctx, q, cache, table, mixed)
+            self.attend(ctx, q, cache, table, mixed, gate)
             return self.out.delta(ctx, mixed, "attention.out")
         if (cache.writes and not ctx.decode and x.dtype == torch.bfloat16
                 and api.gemm_tcgen05_qkv_rope_takes(x, self.qkv.weight, self.head_dim, rot.rotary_dim)):
@@ -216,15 +281,22 @@ class CausalAttention(Mixer):
             return None
         return ctx.workspace.get_zeroed("attention.tickets", (max(ctx.sequences * self.kv_heads, 64),), torch.int32)
 
-    def attend(self, ctx, q, cache, table, mixed) -> None:
+    @property
+    def shaped_scores(self) -> bool:
+        """Capped scores or a distance bias: what only the exact kernel applies."""
+        return self.softcap > 0.0 or self.slopes is not None
+
+    def attend(self, ctx, q, cache, table, mixed, gate=None) -> None:
         """Prompts in bfloat16 with head size 64 or 128: the tcgen05 kernel.  Other bfloat16
         sizes up to 128 and all decoding: the mma.sync kernels.  Everything else (float32,
         head sizes 48, 80, 144 ..., values of another size than the keys): the exact kernel.
         Sinks go with the tcgen05 prompt kernel, the mma.sync decode kernel and the exact kernel."""
-        same = self.value_dim == self.head_dim
+        same = self.value_dim == self.head_dim and not self.shaped_scores
         if same and not ctx.decode and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim):
             api.attention_tcgen05(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                                   self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status, sinks=self.sinks)
+            if gate is not None:
+                api.sigmoid_gate(mixed, gate, self.value_dim if self.gate == "head" else 0)
             return
         tensor_cores = (same and api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
                         and (self.sinks is None or ctx.decode))
@@ -238,7 +310,13 @@ class CausalAttention(Mixer):
                               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
                               one_token_each=ctx.decode, tickets=self.tickets(ctx, splits) if ctx.decode else None,
                               sinks=self.sinks if ctx.decode else None)
+            if gate is not None:
+                api.sigmoid_gate(mixed, gate, self.value_dim if self.gate == "head" else 0)
         else:
+            if self.window:                     # a window bounds the keys a slice can hold
+                splits = max(1, min(splits, self.window // 64))
+                part_acc, part_ml = self.slice_scratch(ctx, splits)
             api.attention(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                           self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
-                          value_dim=self.value_dim, sinks=self.sinks)
+                          value_dim=self.value_dim, sinks=self.sinks, softcap=self.softcap, slopes=self.slopes, gate=gate,
+                          gate_per_head=self.gate == "head")

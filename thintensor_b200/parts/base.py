@@ -22,6 +22,8 @@ Roles and what each must provide:
   (the previous token, say).  ``Head``: ``forward(ctx, x) -> logits``.
 * ``InputShift``: ``forward(ctx, x, states) -> tensor``: what a mixer reads instead of the normed rows themselves
   (a blend with the previous token's rows, kept as a per-sequence state).
+* ``SideInput``: ``forward(ctx, residual, pending) -> Delta``: what a layer adds at its end from the stream itself and the
+  step's tokens (a gated slice of a second token embedding, say).
 * ``DepthMix``: the weights with which a layer's end mixes the results of the layers so far (``weights()`` only; the
   arrangement hands them to the norm that follows).
 * ``Arrangement``: wires norms, mixer and feed-forward around the residual stream.
@@ -220,6 +222,15 @@ class InputShift(Part):
         raise NotImplementedError
 
 
+class SideInput(Part):
+    """Something a layer adds to the stream at its end that is no function of a norm of the stream: it reads the stream
+    itself (with the layer's last delta added) and the step's tokens.  ``forward(ctx, residual, pending) -> Delta`` adds
+    ``pending`` into the stream and returns what the next norm is to add."""
+
+    def forward(self, ctx, residual: torch.Tensor, pending: "Delta | None") -> "Delta":
+        raise NotImplementedError
+
+
 class Head(Part):
     def forward(self, ctx, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
@@ -290,6 +301,7 @@ FEED_FORWARDS = Registry("feed-forward")
 DEPTH_MIXES = Registry("depth mix")
 EMBEDDINGS = Registry("embedding")
 SHIFTS = Registry("input shift")
+SIDES = Registry("side input")
 HEADS = Registry("head")
 ARRANGEMENTS = Registry("arrangement")
 
@@ -301,6 +313,7 @@ REGISTRIES = {
     "depth": DEPTH_MIXES,
     "embedding": EMBEDDINGS,
     "shift": SHIFTS,
+    "side": SIDES,
     "head": HEADS,
     "arrangement": ARRANGEMENTS,
 }

@@ -96,12 +96,13 @@ class PairHashEmbedding(TokenEmbedding):
 class LinearHead(Head):
     """``fallback`` is the checkpoint name of the tensor that serves as the head when
     the checkpoint stores none (the embedding table); with ``tied`` it is used even if
-    a head is stored."""
+    a head is stored.  ``scale`` multiplies the logits."""
 
     def __init__(self, hidden: int, vocab: int, fallback: str | None = None, tied: bool = False, bias: bool = False,
-                 name: str = "weight"):
+                 name: str = "weight", scale: float = 1.0):
         self.hidden, self.vocab, self.fallback, self.tied, self.bias = int(hidden), int(vocab), fallback, bool(tied), bool(bias)
         self.name = name
+        self.scale = float(scale)                # the logits are multiplied by it
         self.linear: Linear | None = None
 
     def weights(self) -> dict[str, WeightDecl]:
@@ -124,6 +125,7 @@ class LinearHead(Head):
         product could write there, else in scratch memory."""
         into = ctx.logits_out if ctx.logits_out is not None and ctx.logits_out.shape[0] == x.shape[0] else None
         logits = self.linear(ctx, x, "head.logits", into)
-        if logits.shape[0] == 1:
-            return logits[0]
-        return logits.sum(dim=0)
+        logits = logits[0] if logits.shape[0] == 1 else logits.sum(dim=0)
+        if self.scale != 1.0:
+            logits.mul_(self.scale)             # in place: the step's own output tensor stays the one that holds them
+        return logits

@@ -7,6 +7,11 @@ rest are one rotated key part that all heads share.  Per head ``k = [W_uk c | k_
 score is ``(q . k) * scale`` over the last ``window`` positions (or all of them), softmax, then ``W_o`` on the
 concatenated heads.
 
+Options: no low-rank query path at all (``q_rank`` None: ``q = W_q x``, tensor ``q``); a rotation that pairs neighbouring
+numbers and multiplies cosines and sines by a constant (the position encoding's ``interleaved`` and
+``attention_scaling``); every head's output multiplied by ``sigmoid(W_g x)_h``, one number per head (``gate="head"``).  Where
+the queries are projected directly, ONE product makes ``[kv latent | shared key part | queries | gate]``.
+
 Only ``[c | k_rot]`` is cached: one row per token, one key/value head, no value pool.  Decoding (and every step
 the tensor-core kernels do not take) never forms keys or values: the kernel folds ``W_uk`` into the query
 (``a = W_uk_h^T q_h``, so that ``q_h . W_uk_h c = a . c``) and applies ``W_uv_h`` once to the softmax-weighted sum of
@@ -31,12 +36,17 @@ from .spec import PartSpec
 @MIXERS.register("latent_attention")
 class LatentAttention(Mixer):
     NAMES = {"dq": "q_a_proj.weight", "dq_norm": "q_a_norm.weight", "uq": "q_b_proj.weight", "dkv": "kv_a_proj.weight",
-             "dkv_norm": "kv_a_norm.weight", "uk": "k_b_proj.weight", "uv": "v_b_proj.weight", "o": "o_proj.weight"}
+             "dkv_norm": "kv_a_norm.weight", "uk": "k_b_proj.weight", "uv": "v_b_proj.weight", "o": "o_proj.weight",
+             "q": "q_proj.weight", "g": "g_proj.weight"}
 
-    def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int, kv_rank: int, scale: float,
-                 eps: float, position: PartSpec | None = None, window: int | None = None, names: dict | None = None):
+    def __init__(self, hidden: int, heads: int, dim: int, rot_dim: int, value_dim: int, q_rank: int | None, kv_rank: int, scale: float,
+                 eps: float, position: PartSpec | None = None, window: int | None = None, names: dict | None = None,
+                 gate: str | None = None):
         self.hidden, self.heads, self.dim, self.rot_dim = int(hidden), int(heads), int(dim), int(rot_dim)
-        self.value_dim, self.q_rank, self.kv_rank = int(value_dim), int(q_rank), int(kv_rank)
+        self.value_dim, self.q_rank, self.kv_rank = int(value_dim), int(q_rank or 0), int(kv_rank)
+        if gate not in (None, "head"):
+            raise ValueError(f"latent attention gates its heads ('head') or nothing, not {gate!r}")
+        self.gate = gate
         self.scale, self.eps = float(scale), float(eps)
         self.window = None if not window else int(window)
         if self.kv_rank > api.LATENT_MAX_RANK or self.kv_rank + self.rot_dim > api.LATENT_MAX_ROW or self.dim > api.LATENT_MAX_DIM:
@@ -54,14 +64,19 @@ class LatentAttention(Mixer):
 
     def weights(self) -> dict[str, WeightDecl]:
         n = self.names
+        if self.q_rank:
+            queries = {n["dq"]: WeightDecl((self.q_rank, self.hidden)), n["dq_norm"]: WeightDecl((self.q_rank,), init="norm"),
+                       n["uq"]: WeightDecl((self.heads * (self.dim + self.rot_dim), self.q_rank))}
+        else:
+            queries = {n["q"]: WeightDecl((self.heads * (self.dim + self.rot_dim), self.hidden))}
+        gate = {n["g"]: WeightDecl((self.heads, self.hidden))} if self.gate else {}
         return {
-            n["dq"]: WeightDecl((self.q_rank, self.hidden)),
-            n["dq_norm"]: WeightDecl((self.q_rank,), init="norm"),
-            n["uq"]: WeightDecl((self.heads * (self.dim + self.rot_dim), self.q_rank)),
+            **queries,
             n["dkv"]: WeightDecl((self.kv_rank + self.rot_dim, self.hidden)),
             n["dkv_norm"]: WeightDecl((self.kv_rank,), init="norm"),
             n["uk"]: WeightDecl((self.heads * self.dim, self.kv_rank)),
             n["uv"]: WeightDecl((self.heads * self.value_dim, self.kv_rank)),
+            **gate,
             n["o"]: WeightDecl((self.hidden, self.heads * self.value_dim)),
         }
 
@@ -77,26 +92,31 @@ class LatentAttention(Mixer):
         self.position.bind({}, dtype, device)
         if self.position.kind == "rotary":
             self.rot = self.position.rotary()
-            if self.rot.interleaved or self.rot.attention_scaling != 1.0:
-                raise ValueError("latent attention rotates halves of the rotated part and does not scale the rotation")
             if self.rot.rotary_dim % 2 or self.rot.rotary_dim > self.rot_dim:
                 raise ValueError(f"the rotation takes an even number of at most {self.rot_dim} numbers, got {self.rot.rotary_dim}")
         else:
             self.rot = RotaryTable(torch.zeros(1, dtype=torch.float32, device=device), 0, 1.0)
         n = self.names
-        self.down = Linear(torch.cat([tensors[n["dq"]], tensors[n["dkv"]]], dim=0))     # [q latent | kv latent | shared key part]
-        self.up_q = Linear(tensors[n["uq"]])
+        if self.q_rank:
+            rows = [tensors[n["dq"]], tensors[n["dkv"]]]                    # [q latent | kv latent | shared key part]
+            self.up_q = Linear(tensors[n["uq"]])
+            self.q_norm = tensors[n["dq_norm"]].to(torch.float32).contiguous()
+        else:
+            rows = [tensors[n["dkv"]], tensors[n["q"]]]                     # [kv latent | shared key part | queries]
+            self.up_q, self.q_norm = None, None
+        if self.gate:
+            rows.append(tensors[n["g"]])                                    # one gate number per head behind everything else
+        self.down = Linear(torch.cat(rows, dim=0))
         self.out = Linear(tensors[n["o"]])
-        self.q_norm = tensors[n["dq_norm"]].to(torch.float32).contiguous()
         self.kv_norm = tensors[n["dkv_norm"]].to(torch.float32).contiguous()
         self.w_key, self.w_value = tensors[n["uk"]].contiguous(), tensors[n["uv"]].contiguous()
         self.expander = Linear(torch.cat([self.w_key, self.w_value], dim=0))        # [W_uk; W_uv]: a latent into all heads' keys and values
 
     def projections(self) -> list:
-        return [self.down, self.up_q, self.expander, self.out]
+        return [p for p in (self.down, self.up_q, self.expander, self.out) if p is not None]
 
     def vectors(self) -> list[torch.Tensor]:
-        return [self.q_norm, self.kv_norm]
+        return [v for v in (self.q_norm, self.kv_norm) if v is not None]
 
     def device_driven(self) -> bool:
         return True
@@ -107,14 +127,21 @@ class LatentAttention(Mixer):
         table = ctx.tables[cache.group]
         rot = self.rot
         down = self.down(ctx, x, "latent.down")
-        q_latent = ctx.scratch("latent.q_latent", (ctx.n_tokens, self.q_rank))
-        api.latent_prepare(down, self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm, self.eps, rot.inv_freq,
+        front = self.q_rank + self.kv_rank + self.rot_dim
+        head_gate = down[:, :, down.shape[2] - self.heads:] if self.gate else None
+        q_latent = ctx.scratch("latent.q_latent", (ctx.n_tokens, self.q_rank)) if self.q_rank else None
+        api.latent_prepare(down[:, :, :front], self.q_rank, self.kv_rank, self.rot_dim, self.q_norm, self.kv_norm, self.eps, rot.inv_freq,
                            rot.rotary_dim, q_latent, cache.k_pool if cache.writes else None, table, ctx.cu, ctx.len_before,
-                           ctx.sequences, ctx.n_tokens, ctx.status)
-        q = self.up_q(ctx, q_latent, "latent.up_q")
+                           ctx.sequences, ctx.n_tokens, ctx.status, interleaved=rot.interleaved, rot_scale=rot.attention_scaling)
+        if self.q_rank:
+            q = self.up_q(ctx, q_latent, "latent.up_q")
+        else:
+            q = down[:, :, front:front + self.heads * (self.dim + self.rot_dim)]
         mixed = ctx.scratch("latent.mixed", (ctx.n_tokens, self.heads * self.value_dim))
         if self.expands(ctx, x):
             self.attend_expanded(ctx, q, cache, table, mixed)
+            if head_gate is not None:
+                api.sigmoid_gate(mixed, head_gate, self.value_dim)
             return self.out.delta(ctx, mixed, "latent.out")
         splits, tensor_cores = 1, False
         reach = ctx.max_total if self.window is None else min(self.window, ctx.max_total)
@@ -130,7 +157,8 @@ class LatentAttention(Mixer):
         part_ml = ctx.scratch("latent.part_ml", (ctx.n_tokens * self.heads * splits * 2,), torch.float32)
         api.latent_attention(q, self.w_key, self.w_value, cache.k_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens,
                              self.heads, self.dim, self.rot_dim, self.value_dim, self.kv_rank, rot.inv_freq, rot.rotary_dim, self.scale,
-                             self.window or 0, splits, mixed, absorbed, part_acc, part_ml, ctx.status, tensor_cores)
+                             self.window or 0, splits, mixed, absorbed, part_acc, part_ml, ctx.status, tensor_cores,
+                             interleaved=rot.interleaved, rot_scale=rot.attention_scaling, head_gate=head_gate)
         return self.out.delta(ctx, mixed, "latent.out")
 
     # ------------------------------------------------------------ prompts on the tensor cores
@@ -162,6 +190,6 @@ class LatentAttention(Mixer):
         api.latent_scatter(expanded, self.heads, self.dim, self.rot_dim, self.value_dim, keys, values)
         queries = ctx.scratch("latent.queries", (ctx.n_tokens, self.heads * head))
         api.latent_queries(q, self.heads, self.dim, self.rot_dim, self.rot.inv_freq, self.rot.rotary_dim, ctx.cu, ctx.len_before,
-                           ctx.sequences, ctx.n_tokens, queries)
+                           ctx.sequences, ctx.n_tokens, queries, interleaved=self.rot.interleaved, rot_scale=self.rot.attention_scaling)
         api.attention_tcgen05(queries, keys, values, table_tmp, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads, self.heads,
                               head, self.scale, self.window or 0, mixed, ctx.status)

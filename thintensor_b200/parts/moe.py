@@ -6,6 +6,13 @@ score is the largest score in it, and only experts of the ``keep`` best groups c
 ``top`` largest of those, weighted by score / (sum of the chosen scores + 1e-20).  A shared expert of its own width
 runs for every token and is added unweighted.
 
+Options: ``score="sigmoid"`` (scores are the logits' sigmoids); ``correction`` (a stored number per expert that is added to
+the scores for the choice of groups and experts only); ``group_score="top2"`` (a group's score is the sum of its two largest
+choice scores); ``renormalize`` off (the weights are the chosen scores as they are); ``activation="clamped"``: an expert is
+``down(g' sigmoid(alpha g') (u' + 1))`` with ``g' = min(gate x, limit)`` and ``u' = clamp(up x, -limit, limit)``, the shared expert
+with a limit of its own; ``shared_gate``: the shared expert's output is multiplied by ``sigmoid(w_sg . x)``, one number a token,
+whose row rides behind the router's rows in one product.
+
 The experts run as ONE gated product over the concatenation of all experts' gate and up rows (the shared expert's
 behind them) and ONE down product over the concatenated columns: a token's activations are multiplied by its
 routing weight per expert (zero for experts it did not choose) in between, so the down product's sum over its input
@@ -25,14 +32,22 @@ from .linear import GatedLinear, Linear
 @FEED_FORWARDS.register("moe")
 class MixtureOfExperts(FeedForward):
     NAMES = {"router": "router.weight", "expert": "experts.{}.", "shared": "shared.", "gate": "gate_proj.weight", "up": "up_proj.weight",
-             "down": "down_proj.weight"}
+             "down": "down_proj.weight", "correction": "router.correction", "shared_gate": "shared.gate.weight"}
 
     def __init__(self, hidden: int, experts: int, top: int, inter: int, groups: int = 1, keep: int = 1, shared_inter: int = 0,
-                 activation: str = "silu", names: dict | None = None):
+                 activation: str = "silu", names: dict | None = None, score: str = "softmax", correction: bool = False,
+                 group_score: str = "max", renormalize: bool = True, limit: float = 0.0, shared_limit: float = 0.0, alpha: float = 1.702,
+                 shared_gate: bool = False):
         self.hidden, self.experts, self.top, self.inter = int(hidden), int(experts), int(top), int(inter)
         self.groups, self.keep, self.shared_inter = int(groups), int(keep), int(shared_inter or 0)
-        if activation not in api.GATE_ACTIVATIONS:
-            raise ValueError(f"gate activation {activation!r} is not one of {sorted(api.GATE_ACTIVATIONS)}")
+        if activation != "clamped" and activation not in api.GATE_ACTIVATIONS:
+            raise ValueError(f"gate activation {activation!r} is not 'clamped' or one of {sorted(api.GATE_ACTIVATIONS)}")
+        if score not in ("softmax", "sigmoid") or group_score not in ("max", "top2"):
+            raise ValueError("routing scores are 'softmax' or 'sigmoid', group scores 'max' or 'top2'")
+        self.score, self.group_score, self.renormalize = score, group_score, bool(renormalize)
+        self.has_correction, self.shared_gate = bool(correction), bool(shared_gate) and bool(shared_inter)
+        self.limit, self.shared_limit, self.alpha = float(limit or 0.0), float(shared_limit or 0.0), float(alpha)
+        self.correction: torch.Tensor | None = None
         if self.experts % self.groups or not 1 <= self.keep <= self.groups:
             raise ValueError(f"{experts} experts do not form {groups} equal groups of which {keep} stay")
         if not 1 <= self.top <= self.keep * (self.experts // self.groups):
@@ -63,15 +78,24 @@ class MixtureOfExperts(FeedForward):
             out[up] = WeightDecl((inter, self.hidden))
             out[down] = WeightDecl((self.hidden, inter))
         out[self.names["router"]] = WeightDecl((self.experts, self.hidden))
+        if self.has_correction:
+            out[self.names["correction"]] = WeightDecl((self.experts,), init="small")
+        if self.shared_gate:
+            out[self.names["shared_gate"]] = WeightDecl((1, self.hidden))
         return out
 
     def bind(self, tensors, dtype, device) -> None:
         names = [self._expert_names(prefix) for prefix, _ in self._prefixes()]
         self.gate_up = GatedLinear(torch.cat([tensors[g] for g, _, _ in names], dim=0), torch.cat([tensors[u] for _, u, _ in names], dim=0),
-                                   None, None, self.activation)
+                                   None, None, "silu" if self.activation == "clamped" else self.activation)
         self.down = Linear(torch.cat([tensors[d] for _, _, d in names], dim=1))
         # the router's sums are float32 in both dtypes; its matrix stays as stored (widening bfloat16 changes nothing)
-        self.router = Linear(tensors[self.names["router"]])
+        router = tensors[self.names["router"]]
+        if self.shared_gate:                    # the shared expert's gate row behind the experts' rows
+            router = torch.cat([router, tensors[self.names["shared_gate"]].reshape(1, self.hidden).to(router.dtype)], dim=0)
+        self.router = Linear(router)
+        if self.has_correction:
+            self.correction = tensors[self.names["correction"]].to(torch.float32).contiguous()
 
     def projections(self) -> list:
         return [self.router, self.gate_up.fused, self.down]
@@ -81,15 +105,25 @@ class MixtureOfExperts(FeedForward):
 
     def forward(self, ctx, x) -> Delta:
         tokens = ctx.n_tokens
-        gates = ctx.scratch("moe.gates", (tokens, self.experts), torch.float32)
+        extra = 1 if self.shared_gate else 0
+        gates = ctx.scratch("moe.gates", (tokens, self.experts + extra), torch.float32)
         chosen = ctx.scratch("moe.chosen", (tokens, self.top), torch.int32)
         weights = ctx.scratch("moe.weights", (tokens, self.top), torch.float32)
-        if api.route_rows_takes(self.hidden, self.experts):
-            api.route_rows(x, self.router.weight, self.top, self.groups, self.keep, gates, chosen, weights)
+        options = {"score": self.score, "correction": self.correction, "group_score": self.group_score, "renormalize": self.renormalize,
+                   "extra": extra}
+        if api.route_rows_takes(self.hidden, self.experts + extra):
+            api.route_rows(x, self.router.weight, self.top, self.groups, self.keep, gates, chosen, weights, **options)
         else:                                   # rows too wide to stage: the exact product, then the routing
-            logits = ctx.scratch("moe.router", (1, tokens, self.experts), torch.float32)
+            logits = ctx.scratch("moe.router", (1, tokens, self.experts + extra), torch.float32)
             api.gemm_simt(x, self.router.weight, None, logits)
-            api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights)
+            api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights, **options)
+        if self.activation == "clamped":        # the clamp, the unit and the routing weights in one pass over the float32 product
+            act = ctx.scratch("moe.gate_up.act", (tokens, self.experts * self.inter + self.shared_inter))
+            api.expert_activation(self.gate_up.fused(ctx, x, "moe.gate_up"), act, self.experts, self.inter, self.shared_inter, self.limit,
+                                  self.shared_limit, self.alpha, gates, self.shared_gate)
+            return self.down.delta(ctx, act, "moe.down")
         act = self.gate_up(ctx, x, "moe.gate_up")
         api.scale_expert_columns(act, self.inter, gates)
+        if extra:
+            raise NotImplementedError("a gated shared expert goes with the clamped unit")
         return self.down.delta(ctx, act, "moe.down")

@@ -26,6 +26,28 @@ def llama3_scale(inv_freq: torch.Tensor, factor: float, low_freq_factor: float, 
     return torch.where(wavelength < original / high_freq_factor, inv_freq, scaled)
 
 
+def yarn_scale(pair: torch.Tensor, theta: float, dims: int, factor: float, original: float, fast: float, slow: float) -> torch.Tensor:
+    """YaRN (Peng, Quesnelle, Fan and Shippole, "YaRN: Efficient Context Window Extension of Large Language Models"): pairs that
+    turn fewer than ``slow`` times over ``original`` positions are slowed down by ``factor``, pairs that turn more than ``fast``
+    times are kept, and the pairs in between are blended linearly in the pair index.  With ``turns(t)`` the (fractional) index of
+    the pair that makes t turns, ``dims ln(original / (2 pi t)) / (2 ln theta)``: ``lo = max(floor(turns(fast)), 0)``,
+    ``hi = min(ceil(turns(slow)), dims - 1)``, ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)`` and
+    ``f_i = theta^(-2i / dims) * (ramp_i / factor + 1 - ramp_i)``.  ``pair``: the pair indices i, in the precision to compute in."""
+    def turns(t: float) -> float:
+        return dims * math.log(original / (2.0 * math.pi * t)) / (2.0 * math.log(theta))
+
+    lo = max(math.floor(turns(fast)), 0)
+    hi = min(math.ceil(turns(slow)), dims - 1)
+    ramp = torch.clamp((pair - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+    freq = theta ** (-2.0 * pair / dims)
+    return freq / factor * ramp + freq * (1.0 - ramp)
+
+
+def yarn_attention_scaling(factor: float) -> float:
+    """What YaRN multiplies cosines and sines by: ``0.1 ln(factor) + 1``."""
+    return 0.1 * math.log(factor) + 1.0
+
+
 @POSITION_ENCODINGS.register("rope")
 class RotaryEncoding(PositionEncoding):
     """``rotary_dim`` numbers at the front of each head are rotated (all of them by
@@ -59,6 +81,10 @@ class RotaryEncoding(PositionEncoding):
             s = self.scaling
             return llama3_scale(inv_freq, float(s["factor"]), float(s["low_freq_factor"]), float(s["high_freq_factor"]),
                                 int(s["original_max_position_embeddings"])).to(torch.float32)
+        if kind == "yarn":
+            s = self.scaling
+            return yarn_scale(index / 2.0, self.theta, self.rotary_dim, float(s["factor"]), float(s["original"]), float(s["fast"]),
+                              float(s["slow"])).to(torch.float32)
         raise ValueError(f"rotary scaling of type {kind!r} is not implemented")
 
     def bind(self, tensors, dtype, device) -> None:

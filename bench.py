@@ -111,6 +111,7 @@ def reference_arm(config: dict, steps: int, warmup: int) -> int:
 FAMALORN_SHAPES = {"1b": "famalorn-w2048", "3b": "famalorn-w3072"}
 NERUZEN_SHAPES = {"1b": "neruzen-w2048", "3b": "neruzen-w3072"}
 SOGIDRA_SHAPES = {"1b": "sogidra-w2048", "3b": "sogidra-w3072"}
+KEREPEL_SHAPES = {"1b": "kerepel-w2048", "3b": "kerepel-w3072"}
 
 
 def neruzen_pair(size: str) -> tuple[dict, dict]:
@@ -120,6 +121,15 @@ def neruzen_pair(size: str) -> tuple[dict, dict]:
     attention.  Every Neruzen layer has the mixture of experts: 16 experts of 1,024 of which a token takes 4, and a shared
     expert of 4,096, so a token's feed-forward is as wide as Famalorn's dense one (8,192)."""
     return json.loads(json.dumps(SHAPES[NERUZEN_SHAPES[size]])), json.loads(json.dumps(SHAPES[FAMALORN_SHAPES[size]]))
+
+
+def kerepel_pair(size: str) -> tuple[dict, dict]:
+    """(Kerepel config.json, Neruzen config.json) of one size from the table of named shapes: the same width, vocabulary and
+    number of layers (six).  Neruzen is the closest model: latent attention, a mixture of experts of the same sizes (16
+    experts of 1,024 of which a token takes 4, a shared expert of 4,096) and the hashed pair table.  Kerepel's latent layers
+    project their queries directly and gate their heads; its attention layers (16 or 24 heads of 128, a window of 1,024, two of
+    the four reading another layer's keys) stand where Neruzen has linear attentions; every other feed-forward is dense (8,192)."""
+    return json.loads(json.dumps(SHAPES[KEREPEL_SHAPES[size]])), json.loads(json.dumps(SHAPES[NERUZEN_SHAPES[size]]))
 
 
 def sogidra_pair(size: str) -> tuple[dict, dict]:
@@ -146,14 +156,15 @@ def famalorn_pair(size: str) -> tuple[dict, dict]:
 def design_bench(args) -> int:
     """``--design famalorn``: prefill and decode of the Famalorn design beside the Llama decoder at equal size (random
     weights, bfloat16), with each step's time by class of kernel against that class's bound.  ``--design neruzen``: the
-    same for the Neruzen design beside Famalorn, ``--design sogidra`` for the Sogidra design beside Llama.  One JSON line."""
+    same for the Neruzen design beside Famalorn, ``--design sogidra`` for the Sogidra design beside Llama, ``--design kerepel``
+    for the Kerepel design beside Neruzen.  One JSON line."""
     import thintensor_b200
     from thintensor_b200.benchmark import class_fractions, measure_classes, measure_decode, measure_prefill
 
     pk = peaks()
     import torch
     names, pair = {"famalorn": (("famalorn", "llama"), famalorn_pair), "neruzen": (("neruzen", "famalorn"), neruzen_pair),
-                   "sogidra": (("sogidra", "llama"), sogidra_pair)}[args.design]
+                   "sogidra": (("sogidra", "llama"), sogidra_pair), "kerepel": (("kerepel", "neruzen"), kerepel_pair)}[args.design]
     out = {"bench": f"{names[0].capitalize()} beside {names[1].capitalize()} at equal width, feed-forward, vocabulary and layers; random weights, bfloat16",
            "prompt_len": args.prompt_len, "batch": args.batch, "peaks": pk, "sizes": {}}
     for size in args.sizes.split(","):
@@ -202,8 +213,8 @@ def main() -> int:
     parser.add_argument("--batch", type=int, default=BATCH, help="with --only decode: sequences decoded together")
     parser.add_argument("--shape", choices=sorted(SHAPE_NAMES), default="1b", help="with --only: layer sizes of another model of the family")
     parser.add_argument("--prompt-len", type=int, default=PROMPT, help="with --only: tokens per prompt (the context is this plus room for the steps)")
-    parser.add_argument("--design", choices=["famalorn", "neruzen", "sogidra"],
-                        help="measure this design beside the closest model the library has at equal size (Famalorn beside Llama, Neruzen beside Famalorn, Sogidra beside Llama) instead of the headline")
+    parser.add_argument("--design", choices=["famalorn", "neruzen", "sogidra", "kerepel"],
+                        help="measure this design beside the closest model the library has at equal size (Famalorn beside Llama, Neruzen beside Famalorn, Sogidra beside Llama, Kerepel beside Neruzen) instead of the headline")
     parser.add_argument("--sizes", default="1b,3b", help="with --design: which sizes (1b: width 2,048; 3b: width 3,072)")
     args = parser.parse_args()
     if args.design:

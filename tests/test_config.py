@@ -73,8 +73,9 @@ def test_config_errors(change, needle):
 
 
 def test_registry():
-    assert supported_architectures() == ["Famalorn", "LlamaForCausalLM", "Neruzen", "Sogidra"]
+    assert supported_architectures() == ["Famalorn", "Kerepel", "LlamaForCausalLM", "Neruzen", "Sogidra"]
     assert resolve_architecture({"architecture": "Sogidra"}).name == "Sogidra"
+    assert resolve_architecture({"architecture": "Kerepel"}).name == "Kerepel"
     assert resolve_architecture({"architecture": "Famalorn"}).name == "Famalorn"
     assert resolve_architecture({"architecture": "Neruzen"}).name == "Neruzen"
     assert resolve_architecture({"architectures": ["LlamaForCausalLM"]}).name == "LlamaForCausalLM"
@@ -112,7 +113,7 @@ def test_named_shapes_are_whole_configurations():
     assert tuple(shapes) == SHAPE_NAMES
     for name, raw in shapes.items():
         arch, config = load_config(raw)
-        if name.startswith(("famalorn", "neruzen", "sogidra")):
+        if name.startswith(("famalorn", "neruzen", "sogidra", "kerepel")):
             assert arch.name == name.split("-")[0].capitalize() and config.width == raw["width"] and config.to_dict() == raw, name
         else:
             assert arch.name == "LlamaForCausalLM" and config.hidden_size == raw["hidden_size"], name

@@ -21,7 +21,7 @@ from pathlib import Path
 
 
 SHAPE_NAMES = ("llama-3.2-1b", "llama-3.2-3b", "llama-3.1-8b", "tiny-a", "tiny-b", "famalorn-w2048", "famalorn-w3072", "neruzen-w2048", "neruzen-w3072",
-               "sogidra-w2048", "sogidra-w3072")     # keys of config/shapes.json
+               "sogidra-w2048", "sogidra-w3072", "kerepel-w2048", "kerepel-w3072")     # keys of config/shapes.json
 
 
 def build_parser() -> argparse.ArgumentParser:

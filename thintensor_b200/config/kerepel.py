@@ -202,7 +202,7 @@ class KerepelConfig:
     layers: tuple[KerepelLayer, ...]
     bigram: PairTable | None = None
     side_dim: int = 0               # token_side.dim; 0: no per-layer token input
-    logit_scale: float = 1.0
+    logit_scale: float | None = None    # None: config.json gives none, the logits stay as they are
     eos_token_ids: tuple[int, ...] = ()
     architecture: str = ARCHITECTURE
 
@@ -253,13 +253,16 @@ class KerepelConfig:
         eos_ids = () if eos is None else tuple(int(e) for e in (eos if isinstance(eos, (list, tuple)) else [eos]))
         return KerepelConfig(_int(raw, "vocab", "the model"), _int(raw, "width", "the model"), _float(norm, "eps", "norm"), tuple(layers),
                              bigram, _int(side, "dim", "token_side") if side else 0,
-                             _float(raw, "logit_scale", "the model") if raw.get("logit_scale") is not None else 1.0, eos_ids)
+                             _float(raw, "logit_scale", "the model") if raw.get("logit_scale") is not None else None, eos_ids)
 
     def to_dict(self) -> dict[str, Any]:
         out: dict[str, Any] = {"architecture": self.architecture}
         if self.bigram is not None:
             out["embedding"] = {"bigram": self.bigram.to_dict()}
-        out.update({"layers": [layer.to_dict() for layer in self.layers], "logit_scale": self.logit_scale, "norm": {"eps": self.eps}})
+        out["layers"] = [layer.to_dict() for layer in self.layers]
+        if self.logit_scale is not None:
+            out["logit_scale"] = self.logit_scale
+        out["norm"] = {"eps": self.eps}
         if self.side_dim:
             out["token_side"] = {"dim": self.side_dim}
         out.update({"vocab": self.vocab, "width": self.width})

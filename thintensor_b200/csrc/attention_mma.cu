@@ -199,7 +199,36 @@ template <int HD, int NQ> struct KeyTileState {
     float o[DT][NQ][4];                 // [0], [1]: dimension 16 dt + g, queries 8 nq + 2 t and + 1; [2], [3]: dimension + 8
     float m_run[NQ][2], l_run[NQ][2];   // queries 8 nq + 2 t + e; l is this lane's share (its keys) until finish_sums
     int pos, first;                     // the step's token sees keys first .. pos
+    // the instances that shape the scores (see DecodeShaping): this lane's queries' slopes, the cap and the scale, in log2 units
+    float slope_log2[NQ][2], cap_log2, into_cap, plain_log2;
 };
+
+// Shaped scores of the decode kernel's SHAPED instances: a scaled score s becomes softcap * tanh(s / softcap) (softcap > 0;
+// the hardware's tanh), and slopes[head] * (query position - key position) is taken off it (slopes: one per query head, or null).
+struct DecodeShaping {
+    float scale, softcap;
+    const float* slopes;
+};
+
+__device__ __forceinline__ float mma_tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD, int NQ>
+__device__ __forceinline__ void start_shaping(KeyTileState<HD, NQ>& st, const DecodeShaping& shaping, int first_head, int group, int t) {
+    st.cap_log2 = shaping.softcap * 1.4426950408889634f;
+    st.into_cap = shaping.softcap > 0.0f ? shaping.scale / shaping.softcap : 0.0f;
+    st.plain_log2 = shaping.scale * 1.4426950408889634f;
+#pragma unroll
+    for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+            const int query = 8 * nq + 2 * t + e;
+            st.slope_log2[nq][e] = (shaping.slopes && query < group) ? __ldg(shaping.slopes + first_head + query) * 1.4426950408889634f : 0.0f;
+        }
+}
 
 template <int HD, int NQ>
 __device__ __forceinline__ void start_queries(KeyTileState<HD, NQ>& st, const __nv_bfloat16* rows, int row_stride, int group, int g, int t,
@@ -222,7 +251,7 @@ __device__ __forceinline__ void start_queries(KeyTileState<HD, NQ>& st, const __
 }
 
 // One block of 64 keys, as four key tiles of 16; load_k and load_v as in block_math.
-template <int HD, int NQ, typename LoadK, typename LoadV>
+template <int HD, int NQ, bool SHAPED = false, typename LoadK, typename LoadV>
 __device__ __forceinline__ void key_tile_math(KeyTileState<HD, NQ>& st, int key_base, int g, int t, float scale_log2,
                                               LoadK load_k, LoadV load_v) {
     constexpr int KC = HD / 32, DT = HD / 16, N_MT = TT_BLOCK_TOKENS / 16;
@@ -240,6 +269,22 @@ __device__ __forceinline__ void key_tile_math(KeyTileState<HD, NQ>& st, int key_
                 mma_bf16(s[m][nq], ka.z, kb.z, ka.w, kb.w, st.q[nq][c][2], st.q[nq][c][3]);
             }
         }
+    }
+    if constexpr (SHAPED) {            // cap and distance bias key by key, into log2 units (scale_log2 is then one)
+#pragma unroll
+        for (int m = 0; m < N_MT; ++m)
+#pragma unroll
+            for (int hi = 0; hi < 2; ++hi) {
+                const float away = (float)(st.pos - (key_base + key_of(2 * m + hi, g)));
+#pragma unroll
+                for (int nq = 0; nq < NQ; ++nq)
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float raw = s[m][nq][2 * hi + e];
+                        const float capped = st.into_cap > 0.0f ? st.cap_log2 * mma_tanh_approx(raw * st.into_cap) : raw * st.plain_log2;
+                        s[m][nq][2 * hi + e] = fmaf(-st.slope_log2[nq][e], away, capped);
+                    }
+            }
     }
     if (!(key_base + TT_BLOCK_TOKENS - 1 <= st.pos && key_base >= st.first)) {     // a sequence's end or a window's edge: key by key
 #pragma unroll
@@ -600,14 +645,14 @@ __device__ __noinline__ void combine_by_last_cta(unsigned* __restrict__ tickets,
 // TICKETS: the instance that can combine more slices than a cluster holds by itself (see combine_by_last_cta).  It
 // is a kernel of its own because the mere presence of that path cost the others' main loop 8 to 28 % (measured on a
 // B200: 0.853 -> 0.92 ms per step at batch 8, 2.09 -> 2.65 ms with 32,768 cached tokens), whether inlined or not.
-template <int HD, bool ROPE, int SHAPE, bool TICKETS = false, int NQ = 1>
+template <int HD, bool ROPE, int SHAPE, bool TICKETS = false, int NQ = 1, bool SHAPED = false>
 __global__ void __launch_bounds__(DecodeShape<HD, SHAPE>::WARPS * 32)
 attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __nv_bfloat16* __restrict__ k_pool,
                         __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ table, int table_width,
                         int pool_blocks, const int* __restrict__ len_before, int heads, int kv_heads, float scale_log2,
                         int window, int splits, int cluster_merge, __nv_bfloat16* __restrict__ out,
                         float* __restrict__ part_acc, float* __restrict__ part_ml, unsigned* __restrict__ tickets, int undelivered_bytes,
-                        unsigned* status, const float* __restrict__ sinks) {
+                        unsigned* status, const float* __restrict__ sinks, const DecodeShaping shaping) {
     constexpr int WARPS = DecodeShape<HD, SHAPE>::WARPS, STAGES = DecodeShape<HD, SHAPE>::STAGES;
     constexpr int TILE = TT_BLOCK_TOKENS * HD * 2;     // bytes of a block's keys of one head, and of its values
     extern __shared__ __align__(128) uint4 slots[];   // [WARPS][STAGES]: a K tile [64 keys][HD], then a V tile [HD][64 keys], as they lie in the cache
@@ -739,6 +784,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
     } else {
         start_queries<HD, NQ>(st, q + ((size_t)b * heads + kh * group) * HD, HD, group, g, t, pos, lo_key);
     }
+    if constexpr (SHAPED) start_shaping<HD, NQ>(st, shaping, kh * group, group, t);
 
     int waited = 0;                                    // blocks of this warp whose copies have been waited for
     for (int i = 0; i < n_mine; ++i) {
@@ -752,7 +798,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, DecodeRope rope, __
         if (!((valid >> (i & 31)) & 1u)) continue;
         const char* src = my_slots + (size_t)(i % STAGES) * 2 * TILE;
         const int kb = my_begin + warp + i * WARPS;
-        key_tile_math<HD, NQ>(st, kb * TT_BLOCK_TOKENS, g, t, scale_log2,
+        key_tile_math<HD, NQ, SHAPED>(st, kb * TT_BLOCK_TOKENS, g, t, SHAPED ? 1.0f : scale_log2,
                               [&](int j, int c) { return *reinterpret_cast<const uint4*>(src + k_lane + ((32 * (j >> 2) + 2 * (j & 3)) * HD * 2 + 64 * c)); },
                               [&](int n, int half) { return *reinterpret_cast<const uint4*>(src + v_lane + (n * 8 * TT_BLOCK_TOKENS * 2 + 64 * half)); });
     }
@@ -863,15 +909,15 @@ inline bool slices_form_cluster(int splits) { return splits > 1 && splits <= 8; 
 
 // The decode kernel, plain (ROPE = false: rotated queries in q, the cache already holds the
 // step's keys and values) or fused with the rotation and the cache write.
-template <int HD, bool ROPE, int SHAPE, int NQ>
+template <int HD, bool ROPE, int SHAPE, int NQ, bool SHAPED = false>
 cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_pool, void* v_pool, const int* table, int table_width,
                                 int pool_blocks, const int* len_before, int sequences, int heads, int kv_heads, float scale_log2,
                                 int window, int splits, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
-                                cudaStream_t stream) {
+                                cudaStream_t stream, const DecodeShaping shaping = DecodeShaping{0.0f, 0.0f, nullptr}) {
     using D = DecodeShape<HD, SHAPE>;
     constexpr int shared = D::WARPS * D::STAGES * (8 * (HD / 32) + (HD / 8) * 2) * 32 * 16;
     static_assert(shared >= D::WARPS * 16 * (HD + 6) * 4 + 16 * (HD + 2) * 4, "the slots must also hold the warps' and the CTA's partial results");
-    if constexpr (SHAPE == ONE_PER_SM) {
+    if constexpr (SHAPE == ONE_PER_SM && !SHAPED) {
         if (tickets && splits > 1 && !slices_form_cluster(splits)) {
             static bool configured_tickets = false;
             auto with_tickets = attention_decode_kernel<HD, ROPE, SHAPE, true, NQ>;
@@ -882,11 +928,11 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
             }
             return tt_launch_pdl(with_tickets, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
                 (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
+                len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks, shaping);
         }
     }
     static bool configured = false;
-    auto kernel = attention_decode_kernel<HD, ROPE, SHAPE, false, NQ>;
+    auto kernel = attention_decode_kernel<HD, ROPE, SHAPE, false, NQ, SHAPED>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, shared);
         if (err != cudaSuccess) return err;
@@ -895,10 +941,10 @@ cudaError_t launch_decode_tiles(const void* q, const DecodeRope& rope, void* k_p
     if (slices_form_cluster(splits))
         return tt_launch_pdl_cluster(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream, (unsigned)splits,
             (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
+            len_before, heads, kv_heads, scale_log2, window, splits, 1, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks, shaping);
     return tt_launch_pdl(kernel, dim3(sequences, kv_heads, splits), dim3(D::WARPS * 32), shared, stream,
         (const __nv_bfloat16*)q, rope, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, table, table_width, pool_blocks,
-        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks);
+        len_before, heads, kv_heads, scale_log2, window, splits, 0, (__nv_bfloat16*)out, part_acc, part_ml, tickets, decode_undelivered_bytes_for_tests, status, sinks, shaping);
 }
 
 // One column tile of 8 queries serves groups of up to 8 query heads per key/value head, two serve up to 16.
@@ -929,10 +975,25 @@ template <int HD>
 int launch(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width, int pool_blocks,
            const int* cu, const int* len_before, int sequences, int n_tokens, int heads, int kv_heads, float scale,
            int window, int splits, int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
-           cudaStream_t stream) {
+           cudaStream_t stream, const DecodeShaping shaping = DecodeShaping{0.0f, 0.0f, nullptr}) {
     const int group = heads / kv_heads;
     const float scale_log2 = scale * 1.4426950408889634f;
     cudaError_t err;
+    const bool shaped = shaping.softcap > 0.0f || shaping.slopes != nullptr;
+    if (shaped && !one_token_each) return (int)cudaErrorInvalidValue;       // shaped scores join the decode kernel only
+    if (shaped) {
+        // one shape of CTA; slices beyond a cluster's go through scratch memory and the merge kernel
+        if (group > 8)
+            err = launch_decode_tiles<HD, false, ONE_PER_SM, 2, true>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
+                                                                      pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
+                                                                      part_acc, part_ml, nullptr, status, sinks, stream, shaping);
+        else
+            err = launch_decode_tiles<HD, false, ONE_PER_SM, 1, true>(q, DecodeRope{}, const_cast<void*>(k_pool), const_cast<void*>(v_pool), table, table_width,
+                                                                      pool_blocks, len_before, sequences, heads, kv_heads, scale_log2, window, splits, out,
+                                                                      part_acc, part_ml, nullptr, status, sinks, stream, shaping);
+        if (err != cudaSuccess) return (int)err;
+        return merge_slices<HD>(n_tokens, heads, splits, out, part_acc, part_ml, stream, slices_form_cluster(splits));
+    }
     if (one_token_each) {
         static int sm_count = 0;
         if (sm_count == 0) {
@@ -1010,13 +1071,14 @@ extern "C" int tt_attention_mma(const void* q, const void* k_pool, const void* v
                                 int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
                                 int heads, int kv_heads, int head_dim, float scale, int window, int splits,
                                 int one_token_each, void* out, float* part_acc, float* part_ml, unsigned* tickets, unsigned* status, const float* sinks,
-                                cudaStream_t stream) {
+                                float softcap, const float* slopes, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
+    const DecodeShaping shaping{scale, softcap, slopes};       // capped scores and a distance bias: the decode kernel's shaped instances
     if (!tt_attention_mma_supports(heads, kv_heads, head_dim) || splits < 1 || splits > 65535 || kv_heads > 65535)
         return (int)cudaErrorInvalidValue;
     if (splits > 1 && (!part_acc || !part_ml)) return (int)cudaErrorInvalidValue;
     if (sinks && !one_token_each) return (int)cudaErrorInvalidValue;      // sinks (one float per query head) join the decode kernel only
-#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, tickets, status, sinks, stream)
+#define TT_LAUNCH(HD) return launch<HD>(q, k_pool, v_pool, table, table_width, pool_blocks, cu, len_before, sequences, n_tokens, heads, kv_heads, scale, window, splits, one_token_each, out, part_acc, part_ml, tickets, status, sinks, stream, shaping)
     switch (head_dim) {
         case 32: TT_LAUNCH(32);
         case 64: TT_LAUNCH(64);

@@ -95,9 +95,23 @@ struct Args {
     __nv_bfloat16* out;
     unsigned* status;
     const float* sinks;     // one per query head, or null: exp(sink) joins the softmax denominator, with no key, no value and no scale
+    // the SHAPED instances only: a scaled score s becomes softcap * tanh(s / softcap) (softcap > 0), slopes[head] * (query
+    // position - key position) is taken off it, and the output is multiplied by the sigmoid of a gate: float32 partial sums
+    // [gate_splits][tokens][gate_row] whose pointer stands at the gate's first column, one number per output number or per head
+    float scale, softcap;
+    const float* slopes;
+    const float* gate;
+    int gate_splits, gate_row, gate_per_head;
+    long long gate_split_stride;
 };
 
-template <int HD>
+__device__ __forceinline__ float tanh_approx(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+template <int HD, bool SHAPED>
 __global__ void __launch_bounds__(Layout<HD>::THREADS, HD == 64 ? 2 : 1)
 attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                          const __grid_constant__ CUtensorMap map_v, const Args args) {
@@ -250,6 +264,13 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
         constexpr int SPLIT = L::SPLIT, HALF_KEYS = KEYS / SPLIT, O_COLS = HD / SPLIT;   // what one thread of a row handles
         float m_used = -INFINITY, l = 0.0f;                       // the scale in use (log2 units) and this thread's part of the sum
         bool ok = true;
+        // shaped scores are brought to log2 units key by key, so the scale that follows is one
+        const float scale_log2 = SHAPED ? 1.0f : args.scale_log2;
+        float slope_log2 = 0.0f, inv_cap = 0.0f;
+        if (SHAPED) {
+            if (args.slopes) slope_log2 = __ldg(args.slopes + kh * args.group + (r - local * args.group)) * 1.4426950408889634f;
+            if (args.softcap > 0.0f) inv_cap = 1.0f / args.softcap;
+        }
         auto pair_barrier = [&]() { if (SPLIT == 2) asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory"); };
         auto expired = [&]() { if (lane == 0) atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); ok = false; };
         for (int i = 0; i < n_blocks; ++i) {
@@ -268,6 +289,15 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                     for (int j = 0; j < 32; ++j) s[32 * c + j] = tmem_loaded(raw[c][j]);
             }
             const int key_base = (block0 + i) * KEYS + half * HALF_KEYS;
+            if (SHAPED) {
+                const float cap_log2 = args.softcap * 1.4426950408889634f, plain_log2 = args.scale * 1.4426950408889634f;
+                const float away = (float)(pos - key_base);                   // the distance to the block's first key
+#pragma unroll
+                for (int j = 0; j < HALF_KEYS; ++j) {
+                    const float capped = inv_cap > 0.0f ? cap_log2 * tanh_approx(s[j] * (args.scale * inv_cap)) : s[j] * plain_log2;
+                    s[j] = fmaf(slope_log2, (float)j - away, capped);
+                }
+            }
             const bool all_visible = __all_sync(0xffffffffu, key_base + HALF_KEYS - 1 <= pos && key_base >= first);
             if (!all_visible) {
 #pragma unroll
@@ -290,7 +320,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 pair_barrier();
                 mx = fmaxf(mx, pair_max[i & 1][half ^ 1][r]);
             }
-            mx *= args.scale_log2;
+            mx *= scale_log2;
             const bool grow = mx > m_used + RESCALE_THRESHOLD || (m_used == -INFINITY && mx != -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? mx : m_used;
@@ -314,7 +344,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             // p = 2^(s * scale - base), two at a time: packed multiply-add, two exponentials, packed sum, one conversion
             // per pair.  (Making a quarter or half of the pairs by a cubic on the floating-point pipes instead of the
             // special-function unit was measured slower: 168 -> 193 and 221 ms for a 32,768-token prompt.)
-            const uint64_t scale2 = pack2(args.scale_log2, args.scale_log2), nbase2 = pack2(-base, -base);
+            const uint64_t scale2 = pack2(scale_log2, scale_log2), nbase2 = pack2(-base, -base);
             uint64_t sum_a = pack2(0.0f, 0.0f), sum_b = sum_a;
             uint32_t packed[HALF_KEYS / 2];
 #pragma unroll
@@ -362,10 +392,31 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             const float inv = l > 0.0f ? 1.0f / l : 0.0f;
             const int token = seq_begin + tok0 + local, head = kh * args.group + (r - local * args.group);
             __nv_bfloat16* dst = args.out + ((size_t)token * args.heads + head) * HD + half * O_COLS;
+            const bool gated = SHAPED && args.gate != nullptr && row_ok;
+            float head_gate = 1.0f;
+            if (gated && args.gate_per_head) {
+                float z = 0.0f;
+                for (int gs = 0; gs < args.gate_splits; ++gs) z += __ldg(args.gate + gs * args.gate_split_stride + (size_t)token * args.gate_row + head);
+                head_gate = 1.0f / (1.0f + __expf(-z));
+            }
 #pragma unroll
             for (int c = 0; c < O_COLS; c += 32) {
                 float o[32];
                 tmem_load32(lane_base + L::O_COL + half * O_COLS + c, o);
+                if (gated) {
+                    if (args.gate_per_head) {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] *= head_gate;
+                    } else {
+                        const float* g = args.gate + (size_t)token * args.gate_row + (size_t)head * HD + half * O_COLS + c;
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) {
+                            float z = 0.0f;
+                            for (int gs = 0; gs < args.gate_splits; ++gs) z += __ldg(g + gs * args.gate_split_stride + e);
+                            o[e] *= 1.0f / (1.0f + __expf(-z));
+                        }
+                    }
+                }
                 if (row_ok) {
 #pragma unroll
                     for (int e = 0; e < 32; e += 8) {
@@ -385,7 +436,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     if (warp == 1) tmem_dealloc(tmem_base, L::TMEM_COLS);
 }
 
-template <int HD>
+template <int HD, bool SHAPED>
 int launch(const void* q, const void* k_pool, const void* v_pool, const Args& args, int n_tokens, cudaStream_t stream) {
     using L = Layout<HD>;
     CUtensorMap map_q, map_k, map_v;
@@ -408,7 +459,7 @@ int launch(const void* q, const void* k_pool, const void* v_pool, const Args& ar
         if (!tc::make_map(&map_v, v_pool, 2, dims, strides, box)) return -1;
     }
     static bool configured = false;
-    auto kernel = attention_tcgen05_kernel<HD>;
+    auto kernel = attention_tcgen05_kernel<HD, SHAPED>;
     if (!configured) {
         const cudaError_t err = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, L::SMEM);
         if (err != cudaSuccess) return (int)err;
@@ -431,7 +482,8 @@ extern "C" int tt_attention_tcgen05_supports(int heads, int kv_heads, int head_d
 extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const void* v_pool, const int* table, int table_width,
                                     int pool_blocks, const int* cu, const int* len_before, int sequences, int n_tokens,
                                     int heads, int kv_heads, int head_dim, float scale, const float* sinks, int window, void* out,
-                                    unsigned* status, cudaStream_t stream) {
+                                    unsigned* status, float softcap, const float* slopes, const float* gate, int gate_splits,
+                                    long long gate_split_stride, int gate_row, int gate_per_head, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (!tt_attention_tcgen05_supports(heads, kv_heads, head_dim) || ((uintptr_t)q & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
         return (int)cudaErrorInvalidValue;
@@ -442,6 +494,12 @@ extern "C" int tt_attention_tcgen05(const void* q, const void* k_pool, const voi
     args.cta_tiles = (n_tokens + args.tokens_per_tile - 1) / args.tokens_per_tile + sequences;   // upper bound; spare CTAs leave at once
     if (args.cta_tiles > 65535) return (int)cudaErrorInvalidValue;                               // the grid's y extent; steps are cut into pieces long before
     args.scale_log2 = scale * 1.4426950408889634f; args.window = window; args.out = (__nv_bfloat16*)out; args.status = status; args.sinks = sinks;
-    if (head_dim == 64) return launch<64>(q, k_pool, v_pool, args, n_tokens, stream);
-    return launch<128>(q, k_pool, v_pool, args, n_tokens, stream);
+    args.scale = scale; args.softcap = softcap; args.slopes = slopes; args.gate = gate; args.gate_splits = gate_splits;
+    args.gate_split_stride = gate_split_stride; args.gate_row = gate_row; args.gate_per_head = gate_per_head;
+    if (softcap > 0.0f || slopes || gate) {         // capped scores, a distance bias or a gate: the instances that shape the scores
+        if (head_dim == 64) return launch<64, true>(q, k_pool, v_pool, args, n_tokens, stream);
+        return launch<128, true>(q, k_pool, v_pool, args, n_tokens, stream);
+    }
+    if (head_dim == 64) return launch<64, false>(q, k_pool, v_pool, args, n_tokens, stream);
+    return launch<128, false>(q, k_pool, v_pool, args, n_tokens, stream);
 }

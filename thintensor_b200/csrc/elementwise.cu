@@ -907,9 +907,9 @@ __global__ void activation_kernel(const float* __restrict__ x, int splits, size_
 extern "C" int tt_activation(const float* x, int splits, long long split_stride, void* act, int act_dtype, long long total,
                              int activation, float a, float c, cudaStream_t stream) {
     if (total <= 0) return 0;
-    if (activation < 0 || activation > 4 || (total & 3)) return (int)cudaErrorInvalidValue;     // rows of whole groups of four
+    if (activation < 0 || activation > 4) return (int)cudaErrorInvalidValue;
     const int threads = 256;
-    const unsigned blocks = (unsigned)((total / 4 + threads - 1) / threads);
+    const unsigned blocks = (unsigned)(((total + 3) / 4 + threads - 1) / threads);      // a thread takes four numbers; the last one what is left
     if (act_dtype == TT_F32)
         tt_launch_pdl(activation_kernel<float>, dim3(blocks), dim3(threads), 0, stream, x, splits, (size_t)split_stride, (float*)act, (size_t)total, activation, a, c);
     else

@@ -417,8 +417,6 @@ def activation(x: torch.Tensor, act: torch.Tensor, activation: str = "gelu_tanh"
     _need(x, torch.float32, "the activation's input")
     if x.dim() != 3 or tuple(act.shape) != tuple(x.shape[1:]) or not act.is_contiguous():
         raise KernelError("activation: the output must be contiguous [tokens, inter] for an input [splits, tokens, inter]")
-    if x.shape[2] % 4:
-        raise KernelError("activation: rows must be whole groups of four numbers")
     fn = _fn("elementwise", "tt_activation", [c_void_p, c_int, c_longlong, c_void_p, c_int, c_longlong, c_int, c_float, c_float, c_void_p])
     _check(fn(_ptr(x), x.shape[0], x.stride(0), _ptr(act), dtype_code(act.dtype), act.numel(), UNARY_ACTIVATIONS[activation], a, c, _stream()),
            "activation")
@@ -597,9 +595,11 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
                   len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
                   scale: float, window: int, splits: int, out: torch.Tensor, part_acc: torch.Tensor | None,
                   part_ml: torch.Tensor | None, status: torch.Tensor, one_token_each: bool = False,
-                  tickets: torch.Tensor | None = None, sinks: torch.Tensor | None = None) -> None:
+                  tickets: torch.Tensor | None = None, sinks: torch.Tensor | None = None, softcap: float = 0.0,
+                  slopes: torch.Tensor | None = None) -> None:
     """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores.
     ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys.
+    ``softcap`` and ``slopes`` (decoding only): see :func:`attention`; the cap's tanh is the hardware's approximation.
     ``tickets`` (decoding; int32, one per sequence and key/value head, zero before the call and after it): with
     more slices than a cluster combines, the CTA that finishes last combines them and no second kernel runs."""
     if not attention_mma_supports(q.dtype, heads, kv_heads, head_dim):
@@ -613,11 +613,21 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
     _check_sinks(sinks, heads)
     if sinks is not None and not one_token_each:
         raise KernelError("the tensor-core kernel of this file takes sinks only when decoding; prompts with sinks run attention_tcgen05 or attention")
+    shaped = bool(softcap) or slopes is not None
+    if shaped and not one_token_each:
+        raise KernelError("the tensor-core kernel of this file shapes scores only when decoding; such prompts run attention_tcgen05 or attention")
+    if slopes is not None:
+        _need(slopes, torch.float32, "slopes")
+        if slopes.numel() != heads:
+            raise KernelError(f"a slope per query head: {heads} numbers, got {slopes.numel()}")
+    if shaped:
+        tickets = None                  # the shaped instances combine slices in a cluster or through the merge kernel
     fn = _fn("attention_mma", "tt_attention_mma", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int,
-                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
+                                                   c_int, c_int, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                   c_float, c_void_p, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
               n_tokens, heads, kv_heads, head_dim, scale, window, splits, sequences if one_token_each else 0, _ptr(out), _ptr(part_acc),
-              _ptr(part_ml), _ptr(tickets), _ptr(status), _ptr(sinks),
+              _ptr(part_ml), _ptr(tickets), _ptr(status), _ptr(sinks), float(softcap or 0.0), _ptr(slopes),
               _stream()), "attention_mma", _attention_launches(splits, one_token_each, tickets is not None))
 
 
@@ -676,18 +686,32 @@ def attention_tcgen05_supports(dtype: torch.dtype, heads: int, kv_heads: int, he
 
 def attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, table: torch.Tensor, cu: torch.Tensor,
                       len_before: torch.Tensor, sequences: int, n_tokens: int, heads: int, kv_heads: int, head_dim: int,
-                      scale: float, window: int, out: torch.Tensor, status: torch.Tensor, sinks: torch.Tensor | None = None) -> None:
+                      scale: float, window: int, out: torch.Tensor, status: torch.Tensor, sinks: torch.Tensor | None = None,
+                      softcap: float = 0.0, slopes: torch.Tensor | None = None, gate: torch.Tensor | None = None,
+                      gate_per_head: bool = False) -> None:
     """Causal attention of packed bfloat16 prompts over the block cache with both products on
-    the tcgen05 tensor cores.  ``sinks``: see :func:`attention`."""
+    the tcgen05 tensor cores.  ``sinks``, ``softcap``, ``slopes``, ``gate``: see :func:`attention` (the cap's tanh is the
+    hardware's approximation here)."""
     _check_sinks(sinks, heads)
+    if slopes is not None:
+        _need(slopes, torch.float32, "slopes")
+        if slopes.numel() != heads:
+            raise KernelError(f"a slope per query head: {heads} numbers, got {slopes.numel()}")
+    g_ptr, g_splits, g_stride, g_row = c_void_p(0), 0, 0, 0
+    if gate is not None:
+        g_ptr, g_splits, g_stride, g_row, g_cols = _projection_view(gate)
+        if g_cols != (heads if gate_per_head else heads * head_dim) or gate.shape[1] != n_tokens:
+            raise KernelError("attention_tcgen05: the gate does not fit the heads")
     if not attention_tcgen05_supports(q.dtype, heads, kv_heads, head_dim):
         raise KernelError(f"the tcgen05 attention kernel does not take {q.dtype}, {heads}/{kv_heads} heads of size {head_dim}")
     if not (k_pool.dtype == v_pool.dtype == out.dtype == torch.bfloat16) or not q.is_contiguous():
         raise KernelError("queries, cache and output must all be contiguous bfloat16")
     fn = _fn("attention_tcgen05", "tt_attention_tcgen05", [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int,
-                                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p])
+                                                           c_int, c_int, c_int, c_int, c_float, c_void_p, c_int, c_void_p, c_void_p, c_float,
+                                                           c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_void_p])
     _check(fn(_ptr(q), _ptr(k_pool), _ptr(v_pool), _ptr(table), table.shape[1], k_pool.shape[0], _ptr(cu), _ptr(len_before), sequences,
-              n_tokens, heads, kv_heads, head_dim, scale, _ptr(sinks), window, _ptr(out), _ptr(status), _stream()), "attention_tcgen05")
+              n_tokens, heads, kv_heads, head_dim, scale, _ptr(sinks), window, _ptr(out), _ptr(status), float(softcap or 0.0), _ptr(slopes),
+              g_ptr, g_splits, g_stride, g_row, 1 if gate_per_head else 0, _stream()), "attention_tcgen05")
 
 
 # --------------------------------------------------------------------------- recurrent

@@ -115,7 +115,7 @@ def describe_kerepel(config: KerepelConfig) -> ModelSpec:
         schedule=tuple(schedule),
         final_norm=norm("final.", "norm"),
         head=PartSpec("linear", {"hidden": config.width, "vocab": config.vocab, "name": "head", "fallback": "embed", "tied": True,
-                                 "scale": config.logit_scale}, ""),
+                                 "scale": 1.0 if config.logit_scale is None else config.logit_scale}, ""),
     )
 
 

@@ -265,7 +265,8 @@ class CausalAttention(Mixer):
         head, slice).  Measured on a B200 from 1 to 64 sequences and 2,048 to 32,768 keys: a step is
         fastest when the slices just fill one wave of one CTA per SM and keep at least 8 blocks each; a
         second wave gains nothing."""
-        return kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.sm_count(ctx.status.device))
+        splits = kv_splits(ctx, ctx.sequences * self.kv_heads, 512, api.sm_count(ctx.status.device))
+        return splits if not self.window else max(1, min(splits, self.window // 512))      # a window bounds the keys there are to slice
 
     def slice_scratch(self, ctx, splits: int):
         """Where the slices of the keys leave their partial results (nothing for one slice)."""
@@ -281,6 +282,8 @@ class CausalAttention(Mixer):
             return None
         return ctx.workspace.get_zeroed("attention.tickets", (max(ctx.sequences * self.kv_heads, 64),), torch.int32)
 
+    TENSOR_CORES_FROM = 1           # packed tokens from which prompts run the tcgen05 kernel
+
     @property
     def shaped_scores(self) -> bool:
         """Capped scores or a distance bias: what only the exact kernel applies."""
@@ -291,15 +294,16 @@ class CausalAttention(Mixer):
         sizes up to 128 and all decoding: the mma.sync kernels.  Everything else (float32,
         head sizes 48, 80, 144 ..., values of another size than the keys): the exact kernel.
         Sinks go with the tcgen05 prompt kernel, the mma.sync decode kernel and the exact kernel."""
-        same = self.value_dim == self.head_dim and not self.shaped_scores
-        if same and not ctx.decode and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim):
+        same = self.value_dim == self.head_dim
+        if (same and not ctx.decode and ctx.n_tokens >= self.TENSOR_CORES_FROM
+                and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)):
+            # capped scores, the distance bias and the gate are the kernel's own (its instances that shape the scores)
             api.attention_tcgen05(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
-                                  self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status, sinks=self.sinks)
-            if gate is not None:
-                api.sigmoid_gate(mixed, gate, self.value_dim if self.gate == "head" else 0)
+                                  self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status, sinks=self.sinks,
+                                  softcap=self.softcap, slopes=self.slopes, gate=gate, gate_per_head=self.gate == "head")
             return
         tensor_cores = (same and api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
-                        and (self.sinks is None or ctx.decode))
+                        and ((self.sinks is None and not self.shaped_scores) or ctx.decode))
         if tensor_cores:
             splits = self.decode_slices(ctx)
         else:
@@ -309,7 +313,7 @@ class CausalAttention(Mixer):
             api.attention_mma(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                               self.kv_heads, self.head_dim, self.scale, self.window or 0, splits, mixed, part_acc, part_ml, ctx.status,
                               one_token_each=ctx.decode, tickets=self.tickets(ctx, splits) if ctx.decode else None,
-                              sinks=self.sinks if ctx.decode else None)
+                              sinks=self.sinks if ctx.decode else None, softcap=self.softcap, slopes=self.slopes)
             if gate is not None:
                 api.sigmoid_gate(mixed, gate, self.value_dim if self.gate == "head" else 0)
         else:

@@ -65,13 +65,14 @@ CONFIGS = {
         "architecture": "Kerepel", "vocab": 160, "width": 128, "norm": {"eps": 1e-6}, "logit_scale": 2.0,
         "embedding": {"bigram": {"buckets": 61, "mul_prev": 3, "mul_cur": 1}}, "token_side": {"dim": 16},
         "layers": [
-            {"type": "attention", "mlp": _moe(4, 1, 48, 0.5, (4, 2), (64, 1.0)), "mixer": {
+            {"type": "attention", "mlp": {"kind": "dense", "ff": 96}, "mixer": {
                 "heads": 4, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 3, "mask": {"size": 100}, "scale": 0.125, "softcap": 40.0}},
             {"type": "latent_attention", "mlp": {"kind": "dense", "ff": 192}, "mixer": {
                 "heads": 2, "dim": 32, "rot_dim": 32, "vdim": 64, "kv_rank": 48, "scale": 0.13, "rot": _yarn(32, 10000.0, 2.0, 64, 16.0, 2.0)}},
             {"type": "attention", "mlp": {"kind": "dense", "ff": 64}, "mixer": {
                 "heads": 2, "kv_heads": 2, "dim": 128, "vdim": 128, "scale": 0.09, "softcap": 25.0}},
-            {"type": "latent_attention", "mlp": None, "mixer": {
+            # the one-choice routing stands last: a close call that rounding decides the other way moves its own position only
+            {"type": "latent_attention", "mlp": _moe(4, 1, 48, 0.5, (4, 2), (64, 1.0)), "mixer": {
                 "heads": 3, "dim": 96, "rot_dim": 32, "vdim": 128, "kv_rank": 72, "scale": 0.1}},
         ],
     },
@@ -94,7 +95,7 @@ def shape_weights(tensors: dict[str, torch.Tensor], seed: int) -> dict[str, torc
         elif leaf in ("mix.q", "mix.k", "mix.dkv"):
             t = t * 25.0
         elif leaf.endswith("router") or leaf.endswith("shared.sg"):
-            t = t * 40.0
+            t = t * 8.0             # sigmoid scores spread over (0, 1): saturated ones would leave the choice to their last bits
         elif leaf.endswith("correction"):
             t = t * 3.0
         elif "norm" in leaf:

@@ -204,22 +204,16 @@ template <int HD, int NQ> struct KeyTileState {
 };
 
 // Shaped scores of the decode kernel's SHAPED instances: a scaled score s becomes softcap * tanh(s / softcap) (softcap > 0;
-// the hardware's tanh), and slopes[head] * (query position - key position) is taken off it (slopes: one per query head, or null).
+// formed with one exponential and one reciprocal), and slopes[head] * (query position - key position) is taken off it (slopes: one per query head, or null).
 struct DecodeShaping {
     float scale, softcap;
     const float* slopes;
 };
 
-__device__ __forceinline__ float mma_tanh_approx(float x) {
-    float y;
-    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
-
 template <int HD, int NQ>
 __device__ __forceinline__ void start_shaping(KeyTileState<HD, NQ>& st, const DecodeShaping& shaping, int first_head, int group, int t) {
     st.cap_log2 = shaping.softcap * 1.4426950408889634f;
-    st.into_cap = shaping.softcap > 0.0f ? shaping.scale / shaping.softcap : 0.0f;
+    st.into_cap = shaping.softcap > 0.0f ? 2.0f * shaping.scale / shaping.softcap * 1.4426950408889634f : 0.0f;    // score -> log2 of exp(2 x / cap)
     st.plain_log2 = shaping.scale * 1.4426950408889634f;
 #pragma unroll
     for (int nq = 0; nq < NQ; ++nq)
@@ -281,7 +275,9 @@ __device__ __forceinline__ void key_tile_math(KeyTileState<HD, NQ>& st, int key_
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float raw = s[m][nq][2 * hi + e];
-                        const float capped = st.into_cap > 0.0f ? st.cap_log2 * mma_tanh_approx(raw * st.into_cap) : raw * st.plain_log2;
+                        // cap tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1): one exponential and one reciprocal
+                        const float capped = st.into_cap > 0.0f ? st.cap_log2 - __fdividef(2.0f * st.cap_log2, fast_exp2(raw * st.into_cap) + 1.0f)
+                                                                : raw * st.plain_log2;
                         s[m][nq][2 * hi + e] = fmaf(-st.slope_log2[nq][e], away, capped);
                     }
             }

@@ -599,7 +599,7 @@ def attention_mma(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, t
                   slopes: torch.Tensor | None = None) -> None:
     """Causal attention of packed bfloat16 query tokens over the block cache on tensor cores.
     ``one_token_each`` (decoding): the warps of a CTA share a sequence's tile and split its keys.
-    ``softcap`` and ``slopes`` (decoding only): see :func:`attention`; the cap's tanh is the hardware's approximation.
+    ``softcap`` and ``slopes`` (decoding only): see :func:`attention`.
     ``tickets`` (decoding; int32, one per sequence and key/value head, zero before the call and after it): with
     more slices than a cluster combines, the CTA that finishes last combines them and no second kernel runs."""
     if not attention_mma_supports(q.dtype, heads, kv_heads, head_dim):
@@ -690,8 +690,7 @@ def attention_tcgen05(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tenso
                       softcap: float = 0.0, slopes: torch.Tensor | None = None, gate: torch.Tensor | None = None,
                       gate_per_head: bool = False) -> None:
     """Causal attention of packed bfloat16 prompts over the block cache with both products on
-    the tcgen05 tensor cores.  ``sinks``, ``softcap``, ``slopes``, ``gate``: see :func:`attention` (the cap's tanh is the
-    hardware's approximation here)."""
+    the tcgen05 tensor cores.  ``sinks``, ``softcap``, ``slopes``, ``gate``: see :func:`attention`."""
     _check_sinks(sinks, heads)
     if slopes is not None:
         _need(slopes, torch.float32, "slopes")

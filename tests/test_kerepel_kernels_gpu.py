@@ -472,3 +472,30 @@ def test_latent_attention_with_direct_queries(dtype, heads, dim, rot, vdim, rank
             held = pool[int(table[b, p // 64]), 0, p % 64].double().cpu()
             assert float((held - cached[b][p]).abs().max()) <= (1e-5 if dtype == torch.float32 else 0.02) * max(1.0, float(cached[b][p].abs().max()))
     assert float(pool[0].min()) == 300.0 and float(pool[int(table[1, 1]), 0, lengths[1] % 64:].min()) == 300.0
+
+
+@pytest.mark.parametrize("tokens", [8, 130, 700])
+def test_clamped_unit_as_the_gated_products_epilogue(tokens):
+    """The tensor-core gated product with the clamped unit as its epilogue and the column scaling behind it, against the
+    plain formula: routed experts' columns with one limit, the shared expert's behind them with another and its own gate."""
+    from thintensor_b200.kernels import api
+
+    g = torch.Generator().manual_seed(tokens)
+    k, experts, width, shared = 64, 5, 24, 40
+    cols = experts * width + shared
+    x = torch.randn(tokens, k, generator=g, dtype=torch.float64).to(torch.bfloat16)
+    w = (torch.randn(2 * cols, k, generator=g, dtype=torch.float64) * 0.3).to(torch.bfloat16)
+    gates = torch.rand(tokens, experts + 1, generator=g, dtype=torch.float64).float()
+    gates[:, :experts][torch.rand(tokens, experts, generator=g) < 0.5] = 0.0
+    act = torch.full((tokens, cols), 9.0, dtype=torch.bfloat16, device=DEV)
+    word = status()
+    api.gemm_tcgen05_clamped(x.to(DEV), w.to(DEV), act, word, 1.0, 2.5, experts * width, 1.702)
+    api.scale_expert_columns(act, width, gates.to(DEV), experts, shared)
+    assert int(word.item()) == 0
+    both = x.double() @ w.double().T
+    gt, up = both[:, :cols], both[:, cols:]
+    limit = torch.cat([torch.full((experts * width,), 1.0), torch.full((shared,), 2.5)]).double()
+    a, u = torch.minimum(gt, limit), torch.maximum(torch.minimum(up, limit), -limit)
+    weight = torch.cat([gates[:, :experts].double().repeat_interleave(width, dim=1), gates[:, experts:].double().expand(tokens, shared)], dim=1)
+    want = a / (1.0 + torch.exp(-1.702 * a)) * (u + 1.0) * weight
+    assert float((act.double().cpu() - want).abs().max()) <= 0.02 * max(1.0, float(want.abs().max()))

@@ -94,7 +94,11 @@ struct Args {
     QkvRope rope;            // qkv form only
     int rope_head_dim;       // 64 or 128
     int undelivered_bytes;   // 0 in every real call; tests: the first stage's barrier expects this many bytes that no copy brings
-    int activation;          // SWIGLU forms: what the gate passes through: 0 silu, 1 relu, 2 the tanh form of gelu
+    int activation;          // SWIGLU forms: what the gate passes through: 0 silu, 1 relu, 2 the tanh form of gelu, 3 the clamped unit
+    // the clamped unit: with g' = min(g, limit) and u' = clamp(u, -limit, limit) the output is g' sigmoid(alpha g') (u' + 1); output
+    // features below clamp_split use clamp_low as their limit, the others clamp_high (a limit of 0 or less: no clamp)
+    float clamp_low, clamp_high, clamp_alpha;
+    int clamp_split;
     unsigned* status;
 };
 
@@ -103,6 +107,16 @@ __device__ __forceinline__ float gate_activation(float g, int activation) {
     if (activation == 1) return fmaxf(g, 0.0f);
     if (activation == 2) return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
     return __fdividef(g, 1.0f + __expf(-g));
+}
+
+// what a gated form stores for output feature `feature`
+__device__ __forceinline__ float gated_unit(float g, float u, int feature, const Args& args) {
+    if (args.activation == 3) {
+        const float limit = feature < args.clamp_split ? args.clamp_low : args.clamp_high;
+        if (limit > 0.0f) { g = fminf(g, limit); u = fminf(fmaxf(u, -limit), limit); }
+        return __fdividef(g, 1.0f + __expf(-args.clamp_alpha * g)) * (u + 1.0f);
+    }
+    return gate_activation(g, args.activation) * u;
 }
 
 // GROUP: k-blocks that share one round of the full / empty barriers (STAGES is a multiple of it).  With few tokens
@@ -266,7 +280,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                         for (int j = 0; j < 16; ++j) {
                             const int token = b_row + c + j;
                             if (token < args.tokens)
-                                out[(size_t)token * args.ld_out + feature] = __float2bfloat16_rn(gate_activation(g[j], args.activation) * exchange[r * PITCH + c + j]);
+                                out[(size_t)token * args.ld_out + feature] = __float2bfloat16_rn(gated_unit(g[j], exchange[r * PITCH + c + j], feature, args));
                         }
                     }
                 }
@@ -303,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             const int f = f0 + j;
-                            if (f < args.features) out[f] = __float2bfloat16_rn(gate_activation(g[j], args.activation) * u[j]);
+                            if (f < args.features) out[f] = __float2bfloat16_rn(gated_unit(g[j], u[j], f, args));
                         }
                     }
                 }
@@ -376,7 +390,7 @@ __device__ __forceinline__ void store_accumulator(uint32_t lane_addr, int token,
 #pragma unroll
                     for (int e = 0; e < 8; ++e) {
                         const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
-                        y[e] = gate_activation(g, args.activation) * u;
+                        y[e] = gated_unit(g, u, f + e, args);
                     }
                     if (vec && f + 8 <= args.features) {
                         const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
@@ -513,7 +527,7 @@ __device__ __forceinline__ void store_swiglu_bulk(uint32_t lane_addr, int first_
 #pragma unroll
             for (int e = 0; e < 8; ++e) {
                 const float g = tmem_loaded(gate[cur][e0 + e]), u = tmem_loaded(up[cur][e0 + e]);
-                y[e] = gate_activation(g, args.activation) * u;
+                y[e] = gated_unit(g, u, f_base + 32 * ci + e0 + e, args);
             }
             const __nv_bfloat162 p0 = __floats2bfloat162_rn(y[0], y[1]), p1 = __floats2bfloat162_rn(y[2], y[3]);
             const __nv_bfloat162 p2 = __floats2bfloat162_rn(y[4], y[5]), p3 = __floats2bfloat162_rn(y[6], y[7]);
@@ -1278,9 +1292,11 @@ static bool deals_k_out(int tiles, int pairs, int k_blocks) {
     return (long long)tiles * 100 < (long long)rounds * pairs * 70;
 }
 
-extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
-                               long long ld_out, long long split_stride, int tokens, int features, int k, int splits,
-                               int form, unsigned* status, cudaStream_t stream, void* shares, long long shares_bytes) {
+struct GateClamp { float low, high, alpha; int split; };
+
+static int gemm_dispatch(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                         long long ld_out, long long split_stride, int tokens, int features, int k, int splits,
+                         int form, unsigned* status, cudaStream_t stream, void* shares, long long shares_bytes, const GateClamp clamp) {
     if (tokens <= 0 || features <= 0) return 0;
     if (k <= 0 || (k % 8) || (ldx % 8) || (ldw % 8) || ((uintptr_t)x & 15) || ((uintptr_t)w & 15) || splits < 1)
         return (int)cudaErrorInvalidValue;
@@ -1288,9 +1304,10 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
     if (splits > k_blocks) splits = k_blocks;
     const int activation = form >> 4;       // the gated form carries its gate's activation in the bits above the form
     form &= 15;
-    if (activation < 0 || activation > 2 || (activation && form != 1)) return (int)cudaErrorInvalidValue;
+    if (activation < 0 || activation > 3 || (activation && form != 1)) return (int)cudaErrorInvalidValue;
     Args args;
     args.activation = activation;
+    args.clamp_low = clamp.low; args.clamp_high = clamp.high; args.clamp_alpha = clamp.alpha; args.clamp_split = clamp.split;
     args.bias = bias; args.out = out; args.ld_out = ld_out; args.split_stride = split_stride;
     args.tokens = tokens; args.features = features; args.k = k;
     args.k_blocks_per_split = (k_blocks + splits - 1) / splits;
@@ -1384,4 +1401,20 @@ extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long
         case 64: return launch<FEATURES_ON_M, 64, 4>(map_a, map_b, args, grid, stream);
         default: return launch<FEATURES_ON_M, 128, 3>(map_a, map_b, args, grid, stream);
     }
+}
+
+extern "C" int tt_gemm_tcgen05(const void* x, long long ldx, const void* w, long long ldw, const float* bias, void* out,
+                               long long ld_out, long long split_stride, int tokens, int features, int k, int splits,
+                               int form, unsigned* status, cudaStream_t stream, void* shares, long long shares_bytes) {
+    return gemm_dispatch(x, ldx, w, ldw, bias, out, ld_out, split_stride, tokens, features, k, splits, form, status, stream, shares, shares_bytes,
+                         GateClamp{0.0f, 0.0f, 1.0f, 0});
+}
+
+// The gated form with the clamped unit as its epilogue (see Args): act[t][f] = g' sigmoid(alpha g') (u' + 1) in bfloat16, with the
+// limit clamp_low for output features below clamp_split and clamp_high for the others.
+extern "C" int tt_gemm_tcgen05_clamped(const void* x, long long ldx, const void* w, long long ldw, void* out, long long ld_out, int tokens,
+                                       int features, int k, float clamp_low, float clamp_high, int clamp_split, float clamp_alpha,
+                                       unsigned* status, cudaStream_t stream) {
+    return gemm_dispatch(x, ldx, w, ldw, nullptr, out, ld_out, 0, tokens, features, k, 1, 1 + 16 * 3, status, stream, nullptr, 0,
+                         GateClamp{clamp_low, clamp_high, clamp_alpha, clamp_split});
 }

@@ -14,8 +14,8 @@
 //
 // tt_expert_activation: the clamped gated unit of every expert's columns times the token's gate for that expert.
 //
-// tt_scale_expert_columns: act[t][e * width + j] *= gates[t][e] for the first experts * width columns of act (the
-// columns behind them, a shared expert's, stay as they are).
+// tt_scale_expert_columns: act[t][e * width + j] *= gates[t][e] for the first experts * width columns of act; the next
+// shared_width columns (an always-on expert's) are multiplied by gates[t][experts], and columns behind those stay as they are.
 #include "common.cuh"
 
 constexpr int ROUTE_MAX_EXPERTS = 512;      // a lane holds ROUTE_MAX_EXPERTS / 32 scores
@@ -211,15 +211,15 @@ __global__ void route_rows_kernel(const TX* __restrict__ x, const TW* __restrict
 
 template <typename T>
 __global__ void scale_expert_columns_kernel(T* __restrict__ act, int row_stride, int width, int experts,
-                                            const float* __restrict__ gates, long long total) {
+                                            const float* __restrict__ gates, int gate_row, int shared_width, long long total) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= total) return;
-    const int per_row = experts * width;
+    const int per_row = experts * width + shared_width;
     const long long t = i / per_row;
     const int c = (int)(i - t * per_row);
-    const float g = gates[t * experts + c / width];
+    const float g = gates[t * gate_row + (c < experts * width ? c / width : experts)];
     T* p = act + t * row_stride + c;
     *p = tt_from_float<T>(tt_to_float(*p) * g);
 }
@@ -240,15 +240,15 @@ extern "C" int tt_route_topk(const float* logits, int splits, long long split_st
 // the same, 16 bytes a thread (width and row_stride are multiples of N numbers)
 template <typename T, int N>
 __global__ void scale_expert_columns_vec_kernel(T* __restrict__ act, int row_stride, int width, int experts,
-                                                const float* __restrict__ gates, long long total) {
+                                                const float* __restrict__ gates, int gate_row, int shared_width, long long total) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * N;
     if (i >= total) return;
-    const int per_row = experts * width;
+    const int per_row = experts * width + shared_width;
     const long long t = i / per_row;
     const int c = (int)(i - t * per_row);
-    const float g = gates[t * experts + c / width];
+    const float g = gates[t * gate_row + (c < experts * width ? c / width : experts)];
     uint4* p = reinterpret_cast<uint4*>(act + t * row_stride + c);
     uint4 raw = *p;
     T* v = reinterpret_cast<T*>(&raw);
@@ -277,26 +277,26 @@ extern "C" int tt_route_rows(const void* x, int x_dtype, const void* w, int w_dt
 }
 
 extern "C" int tt_scale_expert_columns(void* act, int dtype, int n_tokens, int row_stride, int width, int experts, const float* gates,
-                                       cudaStream_t stream) {
-    const long long total = (long long)n_tokens * experts * width;
+                                       int gate_row, int shared_width, cudaStream_t stream) {
+    const long long total = (long long)n_tokens * ((long long)experts * width + shared_width);
     if (total <= 0) return 0;
     const int threads = 256;
     const int n = dtype == TT_F32 ? 4 : 8;
-    if (width % n == 0 && row_stride % n == 0 && ((uintptr_t)act & 15) == 0) {
+    if (width % n == 0 && shared_width % n == 0 && row_stride % n == 0 && ((uintptr_t)act & 15) == 0) {
         const long long blocks = (total / n + threads - 1) / threads;
         if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
         if (dtype == TT_F32)
-            tt_launch_pdl(scale_expert_columns_vec_kernel<float, 4>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)act, row_stride, width, experts, gates, total);
+            tt_launch_pdl(scale_expert_columns_vec_kernel<float, 4>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)act, row_stride, width, experts, gates, gate_row, shared_width, total);
         else
-            tt_launch_pdl(scale_expert_columns_vec_kernel<__nv_bfloat16, 8>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)act, row_stride, width, experts, gates, total);
+            tt_launch_pdl(scale_expert_columns_vec_kernel<__nv_bfloat16, 8>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)act, row_stride, width, experts, gates, gate_row, shared_width, total);
         TT_LAUNCH_CHECK();
     }
     const long long blocks = (total + threads - 1) / threads;
     if (blocks > 2147483647LL) return (int)cudaErrorInvalidValue;
     if (dtype == TT_F32)
-        tt_launch_pdl(scale_expert_columns_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)act, row_stride, width, experts, gates, total);
+        tt_launch_pdl(scale_expert_columns_kernel<float>, dim3((unsigned)blocks), dim3(threads), 0, stream, (float*)act, row_stride, width, experts, gates, gate_row, shared_width, total);
     else
-        tt_launch_pdl(scale_expert_columns_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)act, row_stride, width, experts, gates, total);
+        tt_launch_pdl(scale_expert_columns_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(threads), 0, stream, (__nv_bfloat16*)act, row_stride, width, experts, gates, gate_row, shared_width, total);
     TT_LAUNCH_CHECK();
 }
 

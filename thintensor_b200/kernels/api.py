@@ -1157,15 +1157,20 @@ def route_rows_takes(hidden: int, experts: int) -> bool:
     return (hidden + experts + 32) * 4 <= 48 * 1024 and hidden <= ROUTE_MAX_HIDDEN
 
 
-def scale_expert_columns(act: torch.Tensor, width: int, gates: torch.Tensor) -> None:
+def scale_expert_columns(act: torch.Tensor, width: int, gates: torch.Tensor, experts: int | None = None, shared_width: int = 0) -> None:
     """act[t, e * width + j] *= gates[t, e] for the ``experts * width`` leading columns of ``act`` (in place; columns behind
-    them stay as they are)."""
+    them stay as they are).  ``experts``: fewer than ``gates`` has columns; with ``shared_width`` the next so many columns of
+    ``act`` are multiplied by ``gates[t, experts]`` (the gate of an expert that every token uses)."""
     _need(gates, torch.float32, "gates")
-    tokens, experts = gates.shape
-    if act.dim() != 2 or act.shape[0] != tokens or act.shape[1] < experts * width or act.stride(1) != 1:
+    tokens, columns = gates.shape
+    experts = columns if experts is None else int(experts)
+    if act.dim() != 2 or act.shape[0] != tokens or act.shape[1] < experts * width + shared_width or act.stride(1) != 1:
         raise KernelError("scale_expert_columns: the activations do not fit the gates")
-    fn = _fn("routing", "tt_scale_expert_columns", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(act), dtype_code(act.dtype), tokens, act.stride(0), width, experts, _ptr(gates), _stream()), "scale_expert_columns")
+    if experts > columns or (shared_width and experts >= columns):
+        raise KernelError("scale_expert_columns: too few gates a token")
+    fn = _fn("routing", "tt_scale_expert_columns", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p])
+    _check(fn(_ptr(act), dtype_code(act.dtype), tokens, act.stride(0), width, experts, _ptr(gates), columns, int(shared_width), _stream()),
+           "scale_expert_columns")
 
 
 def expert_activation(gate_up: torch.Tensor, act: torch.Tensor, experts: int, width: int, shared_width: int, limit: float,
@@ -1436,3 +1441,19 @@ def gemm_tcgen05_swiglu(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, sta
                                                  c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong])
     _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(None), _ptr(act), act.stride(0), 0, tokens, inter, k, 1,
               1 + 16 * GATE_ACTIVATIONS[activation], _ptr(status), _stream(), _ptr(None), 0), "gemm_tcgen05_swiglu")
+
+
+def gemm_tcgen05_clamped(x: torch.Tensor, w: torch.Tensor, act: torch.Tensor, status: torch.Tensor, limit: float, shared_limit: float,
+                         split: int, alpha: float) -> None:
+    """:func:`gemm_tcgen05_swiglu` with the clamped unit as its epilogue: with ``g' = min(g, limit)`` and ``u' = clamp(u, -limit,
+    limit)``, ``act[t, f] = g' sigmoid(alpha g') (u' + 1)``; output features below ``split`` use ``limit``, the others
+    ``shared_limit`` (0 or less: no clamp)."""
+    _need(act, torch.bfloat16, "activation output")
+    tokens, k = x.shape
+    inter = w.shape[0] // 2
+    if not gemm_tcgen05_usable(x, w) or w.shape[1] != k or tuple(act.shape) != (tokens, inter):
+        raise KernelError(f"tcgen05 gated gemm cannot take x {tuple(x.shape)} / w {tuple(w.shape)} / act {tuple(act.shape)}")
+    fn = _fn("gemm_tcgen05", "tt_gemm_tcgen05_clamped", [c_void_p, c_longlong, c_void_p, c_longlong, c_void_p, c_longlong, c_int, c_int, c_int,
+                                                         c_float, c_float, c_int, c_float, c_void_p, c_void_p])
+    _check(fn(_ptr(x), x.stride(0), _ptr(w), w.stride(0), _ptr(act), act.stride(0), tokens, inter, k, float(limit or 0.0),
+              float(shared_limit or 0.0), int(split), float(alpha), _ptr(status), _stream()), "gemm_tcgen05_clamped")

@@ -117,10 +117,18 @@ class MixtureOfExperts(FeedForward):
             logits = ctx.scratch("moe.router", (1, tokens, self.experts + extra), torch.float32)
             api.gemm_simt(x, self.router.weight, None, logits)
             api.route_topk(logits, self.top, self.groups, self.keep, gates, chosen, weights, **options)
-        if self.activation == "clamped":        # the clamp, the unit and the routing weights in one pass over the float32 product
+        if self.activation == "clamped":
             act = ctx.scratch("moe.gate_up.act", (tokens, self.experts * self.inter + self.shared_inter))
-            api.expert_activation(self.gate_up.fused(ctx, x, "moe.gate_up"), act, self.experts, self.inter, self.shared_inter, self.limit,
-                                  self.shared_limit, self.alpha, gates, self.shared_gate)
+            w = self.gate_up.fused.weight
+            if api.gemm_tcgen05_usable(x, w) and (tokens > api.SKINNY_TOKENS or api.gemm_tcgen05_splits(tokens, w.shape[0], x.shape[1]) == 1):
+                # the clamp and the unit are the gated product's epilogue (the float32 gate and up never reach memory); the
+                # routing weights and the shared expert's gate then scale the columns in place
+                api.set_label("moe.gate_up")
+                api.gemm_tcgen05_clamped(x, w, act, ctx.status, self.limit, self.shared_limit, self.experts * self.inter, self.alpha)
+                api.scale_expert_columns(act, self.inter, gates, self.experts, self.shared_inter if self.shared_gate else 0)
+            else:                               # the clamp, the unit and the routing weights in one pass over the float32 product
+                api.expert_activation(self.gate_up.fused(ctx, x, "moe.gate_up"), act, self.experts, self.inter, self.shared_inter, self.limit,
+                                      self.shared_limit, self.alpha, gates, self.shared_gate)
             return self.down.delta(ctx, act, "moe.down")
         act = self.gate_up(ctx, x, "moe.gate_up")
         api.scale_expert_columns(act, self.inter, gates)

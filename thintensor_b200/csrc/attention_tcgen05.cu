@@ -284,15 +284,51 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
             }
             const int key_base = (block0 + i) * KEYS + half * HALF_KEYS;
             if (SHAPED) {
-                // cap tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1): one exponential and one reciprocal (the hardware's own
-                // tanh is good to 2^-11 of its value, which at a cap of 50 is 0.02 of a score near the cap)
+                // Otherwise cap tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1), one exponential and one reciprocal (the
+                // hardware's own tanh is good to 2^-11 of its value, which at a cap of 50 is 0.02 of a score near the cap).
                 const float cap_log2 = args.softcap * 1.4426950408889634f, plain_log2 = args.scale * 1.4426950408889634f;
                 const float into_exp = 2.0f * args.scale * inv_cap * 1.4426950408889634f;
                 const float away = (float)(pos - key_base);                   // the distance to the block's first key
+                // Where every score of the warp's rows stays under half the cap (the usual case: a cap is a guard, not a
+                // working point), tanh is its series to y^11 on the floating-point pipes, two scores an instruction, good to
+                // 5e-7 of y there; the special-function unit is the kernel's bound and keeps only the softmax's exponentials.
+                bool small = inv_cap > 0.0f;
+                if (small) {
+                    float hi_a = 0.0f, hi_b = 0.0f;
 #pragma unroll
-                for (int j = 0; j < HALF_KEYS; ++j) {
-                    const float capped = inv_cap > 0.0f ? cap_log2 - __fdividef(2.0f * cap_log2, fast_exp2(s[j] * into_exp) + 1.0f) : s[j] * plain_log2;
-                    s[j] = fmaf(slope_log2, (float)j - away, capped);
+                    for (int j = 0; j < HALF_KEYS; j += 4) {
+                        hi_a = max3(hi_a, fabsf(s[j]), fabsf(s[j + 1]));
+                        hi_b = max3(hi_b, fabsf(s[j + 2]), fabsf(s[j + 3]));
+                    }
+                    small = __all_sync(0xffffffffu, fmaxf(hi_a, hi_b) * (args.scale * inv_cap) <= 0.5f);
+                }
+                if (small) {
+                    const float into_y = args.scale * inv_cap;
+                    const uint64_t y_of = pack2(into_y, into_y), cap2 = pack2(cap_log2, cap_log2), one2 = pack2(1.0f, 1.0f), zero2 = pack2(0.0f, 0.0f);
+                    const uint64_t c3 = pack2(-1.0f / 3.0f, -1.0f / 3.0f), c5 = pack2(2.0f / 15.0f, 2.0f / 15.0f), c7 = pack2(-17.0f / 315.0f, -17.0f / 315.0f);
+                    const uint64_t c9 = pack2(62.0f / 2835.0f, 62.0f / 2835.0f), c11 = pack2(-1382.0f / 155925.0f, -1382.0f / 155925.0f);
+                    const uint64_t step2 = pack2(2.0f * slope_log2, 2.0f * slope_log2);
+                    uint64_t bias2 = pack2(-slope_log2 * away, slope_log2 * (1.0f - away));        // slope * (key - position) of keys j and j + 1
+#pragma unroll
+                    for (int j = 0; j < HALF_KEYS; j += 2) {
+                        const uint64_t y = fma2(pack2(s[j], s[j + 1]), y_of, zero2);
+                        const uint64_t z = fma2(y, y, zero2);
+                        uint64_t p = fma2(c11, z, c9);
+                        p = fma2(p, z, c7);
+                        p = fma2(p, z, c5);
+                        p = fma2(p, z, c3);
+                        p = fma2(p, z, one2);                                  // tanh(y) / y
+                        const uint64_t t = fma2(y, p, zero2);
+                        unpack2(fma2(cap2, t, bias2), s[j], s[j + 1]);
+                        bias2 = add2(bias2, step2);
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < HALF_KEYS; ++j) {
+                        // cap tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1): one exponential and one reciprocal
+                        const float capped = inv_cap > 0.0f ? cap_log2 - __fdividef(2.0f * cap_log2, fast_exp2(s[j] * into_exp) + 1.0f) : s[j] * plain_log2;
+                        s[j] = fmaf(slope_log2, (float)j - away, capped);
+                    }
                 }
             }
             const bool all_visible = __all_sync(0xffffffffu, key_base + HALF_KEYS - 1 <= pos && key_base >= first);

@@ -271,7 +271,8 @@ def test_greedy_generation(folders, name, dtype):
                 margin = float(best.values[0] - logits[token])
                 if dtype == "bfloat16" and float(oracle_sensitivity(folder, sequence)[-1]) > 1e-3:
                     break
-                assert margin < (1e-3 if dtype == "float32" else 0.5), f"{name}: generated {token}, the plain model says {int(best.indices[0])} by {margin}"
+                near = 1e-3 if dtype == "float32" else 0.15 * float(logits.std())        # bfloat16: a small share of the logits' spread
+                assert margin < near, f"{name}: generated {token}, the plain model says {int(best.indices[0])} by {margin}"
                 break
             sequence.append(token)
 

@@ -173,6 +173,10 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
     const int lo_key = (args.window > 0 && lo_pos - args.window + 1 > 0) ? lo_pos - args.window + 1 : 0;
     const int block0 = lo_key / KEYS, block1 = hi_pos / KEYS;
     const int n_blocks = block1 - block0 + 1;
+    // With a distance bias the blocks are walked from the nearest keys back: a row's largest score is then met in its first
+    // blocks, and the accumulator is not rescaled block after block (walking up, a steep head's maximum grew with every block,
+    // and every growth is a round trip of the accumulator through tensor memory that waits for the products before it).
+    const bool walk_back = SHAPED && args.slopes != nullptr;
     tt_pdl_wait();                                                // queries and this step's keys come from the previous kernel
 
     if (warp == 0) {
@@ -191,7 +195,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
                 if (i >= KV_STAGES && !mbar_wait(smem_u32(&kv_empty[s]), (uint32_t)(((i / KV_STAGES) & 1) ^ 1))) {
                     atomicOr(args.status, TT_STATUS_WAIT_EXPIRED); break;
                 }
-                int block = table_row[block0 + i];
+                int block = table_row[walk_back ? block1 - i : block0 + i];
                 if (block < 0 || block >= args.pool_blocks) { atomicOr(args.status, TT_STATUS_BAD_BLOCK); block = 0; }
                 const uint32_t bar = smem_u32(&kv_full[s]);
                 mbar_expect_tx(bar, L::STAGE_BYTES);
@@ -282,7 +286,7 @@ attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid
 #pragma unroll
                     for (int j = 0; j < 32; ++j) s[32 * c + j] = tmem_loaded(raw[c][j]);
             }
-            const int key_base = (block0 + i) * KEYS + half * HALF_KEYS;
+            const int key_base = (walk_back ? block1 - i : block0 + i) * KEYS + half * HALF_KEYS;
             if (SHAPED) {
                 // Otherwise cap tanh(x / cap) = cap - 2 cap / (exp(2 x / cap) + 1), one exponential and one reciprocal (the
                 // hardware's own tanh is good to 2^-11 of its value, which at a cap of 50 is 0.02 of a score near the cap).

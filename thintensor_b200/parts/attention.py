@@ -297,10 +297,14 @@ class CausalAttention(Mixer):
         same = self.value_dim == self.head_dim
         if (same and not ctx.decode and ctx.n_tokens >= self.TENSOR_CORES_FROM
                 and api.attention_tcgen05_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)):
-            # capped scores, the distance bias and the gate are the kernel's own (its instances that shape the scores)
+            # capped scores and the distance bias are the kernel's own (its instances that shape the scores).  So could the gate
+            # be, but a softmax thread owns a row and reads its gate numbers one 32-byte sector a load (measured on a B200:
+            # 2,048 tokens of 16 heads of 128 took 121 us with the gate inside against 50 + 15 us with the pass below)
             api.attention_tcgen05(q, cache.k_pool, cache.v_pool, table, ctx.cu, ctx.len_before, ctx.sequences, ctx.n_tokens, self.heads,
                                   self.kv_heads, self.head_dim, self.scale, self.window or 0, mixed, ctx.status, sinks=self.sinks,
-                                  softcap=self.softcap, slopes=self.slopes, gate=gate, gate_per_head=self.gate == "head")
+                                  softcap=self.softcap, slopes=self.slopes)
+            if gate is not None:
+                api.sigmoid_gate(mixed, gate, self.value_dim if self.gate == "head" else 0)
             return
         tensor_cores = (same and api.attention_mma_supports(q.dtype, self.heads, self.kv_heads, self.head_dim)
                         and ((self.sinks is None and not self.shaped_scores) or ctx.decode))

@@ -77,7 +77,7 @@ def attention_plain(q, keys, values, pos, heads, kv_heads, scale, window, cap, s
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,cap,slope,gate", [
     (4, 1, 64, 64, 72, 50.0, True, "elementwise"), (3, 3, 16, 24, 21, 30.0, True, "elementwise"), (6, 2, 48, 8, 0, 0.0, True, None),
     (2, 2, 20, 36, 64, 5.0, False, "head"), (8, 2, 128, 128, 130, 40.0, True, "elementwise"), (1, 1, 8, 8, 1, 0.0, True, "head"),
-    (5, 5, 32, 32, 65, 20.0, True, None), (6, 2, 64, 64, 100, 30.0, True, "elementwise"), (14, 2, 128, 128, 0, 45.0, True, "head")])
+    (5, 5, 32, 32, 65, 20.0, True, None)])
 def test_attention_marked_keys(dtype, heads, kv_heads, dim, vdim, window, cap, slope, gate):
     """Sequences of unequal lengths, prompts and decoding, through a scrambled table.  In every sequence one key is lined up
     with the last query of head 0: without a window far back or at a block border; with a window just inside the last token's
@@ -499,26 +499,3 @@ def test_clamped_unit_as_the_gated_products_epilogue(tokens):
     weight = torch.cat([gates[:, :experts].double().repeat_interleave(width, dim=1), gates[:, experts:].double().expand(tokens, shared)], dim=1)
     want = a / (1.0 + torch.exp(-1.702 * a)) * (u + 1.0) * weight
     assert float((act.double().cpu() - want).abs().max()) <= 0.02 * max(1.0, float(want.abs().max()))
-
-
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("tokens,hidden,dim", [(1, 96, 8), (5, 200, 24), (8, 1000, 3)])
-def test_side_gate_of_few_tokens_in_one_kernel(dtype, tokens, hidden, dim):
-    """The stream takes the delta, and the gate times the table's slice comes out, as the three-kernel path gives them."""
-    from thintensor_b200.kernels import api
-
-    g = torch.Generator().manual_seed(tokens + hidden)
-    vocab, layers = 19, 3
-    residual = torch.randn(tokens, hidden, generator=g, dtype=torch.float64).float()
-    delta = torch.randn(2, tokens, hidden, generator=g, dtype=torch.float64).float()
-    w = (torch.randn(dim, hidden, generator=g, dtype=torch.float64) / hidden ** 0.5).to(dtype)
-    table = torch.randn(vocab, layers * dim, generator=g, dtype=torch.float64).to(dtype)
-    ids = torch.randint(0, vocab, (tokens,), generator=g).to(torch.int32)
-    for pending in (delta, None):
-        stream, out, word = residual.clone().to(DEV), torch.full((tokens, dim), 9.0, dtype=dtype, device=DEV), status()
-        api.side_gate_rows(stream, None if pending is None else pending.to(DEV), w.to(DEV), table.to(DEV), 2 * dim, ids.to(DEV), out, word)
-        x = residual.double() + (0.0 if pending is None else pending.double().sum(0))
-        assert int(word.item()) == 0 and float((stream.double().cpu() - x).abs().max()) < 1e-6
-        z = x.to(dtype).double() @ w.double().T
-        want = 0.5 * z * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (z + 0.044715 * z ** 3))) * table.double()[ids.long()][:, 2 * dim:3 * dim]
-        assert float((out.double().cpu() - want).abs().max()) <= (2e-6 if dtype == torch.float32 else 0.01) * max(1.0, float(want.abs().max()))

@@ -1197,68 +1197,3 @@ extern "C" int tt_sigmoid_gate(void* y, int dtype, int n_tokens, int cols, const
         tt_launch_pdl(sigmoid_gate_kernel<__nv_bfloat16>, dim3(blocks), dim3(threads), 0, stream, (__nv_bfloat16*)y, cols, gate, splits, (size_t)split_stride, gate_row, head_width, total);
     TT_LAUNCH_CHECK();
 }
-
-// ------------------------------------------------------------------------------------
-// The side gate of a step of few tokens in one kernel, one block per token: the stream takes the pending delta
-// (residual[t] += delta[0][t] + delta[1][t] + ...), the row is narrowed to the activation dtype as a matrix product's operand
-// would be, every warp takes rows of the gate's matrix [dim][hidden] in turn (lanes across the row, float32 sums), and
-// out[t][i] = gelu_tanh(w[i] . x) * table[tokens[t]][col_off + i].  What tt_add_narrow, the gate's product and
-// tt_token_side_gate do in three launches for prompts.
-// ------------------------------------------------------------------------------------
-template <typename TAct, typename TW, typename TT>
-__global__ void side_gate_rows_kernel(float* __restrict__ residual, const float* __restrict__ delta, int splits, size_t split_stride,
-                                      const TW* __restrict__ w, int hidden, int dim, const TT* __restrict__ table, int vocab,
-                                      int table_cols, int col_off, const int* __restrict__ tokens, TAct* __restrict__ out,
-                                      unsigned* status) {
-    tt_pdl_launch_dependents();
-    tt_pdl_wait();
-    extern __shared__ float side_row[];                         // hidden
-    const int t = blockIdx.x;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, warps = blockDim.x >> 5;
-    float* res = residual + (size_t)t * hidden;
-    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
-        float x = res[j];
-        if (splits > 0) {
-            for (int s = 0; s < splits; ++s) x += __ldg(delta + s * split_stride + (size_t)t * hidden + j);
-            res[j] = x;
-        }
-        side_row[j] = tt_to_float(tt_from_float<TAct>(x));
-    }
-    __syncthreads();
-    const int id = tokens[t];
-    const bool known = id >= 0 && id < vocab;
-    if (!known && threadIdx.x == 0) atomicOr(status, TT_STATUS_BAD_TOKEN);
-    for (int i = warp; i < dim; i += warps) {
-        const TW* row = w + (size_t)i * hidden;
-        float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-        int j = lane;
-        for (; j + 96 < hidden; j += 128) {                     // four loads in flight, four sums
-            float v[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q) v[q] = tt_to_float(row[j + 32 * q]);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) a[q] = fmaf(v[q], side_row[j + 32 * q], a[q]);
-        }
-        for (; j < hidden; j += 32) a[0] = fmaf(tt_to_float(row[j]), side_row[j], a[0]);
-        const float z = tt_warp_sum((a[0] + a[1]) + (a[2] + a[3]));
-        if (lane == 0)
-            out[(size_t)t * dim + i] = tt_from_float<TAct>(known ? tt_gate_activation(z, 2) * tt_to_float(table[(size_t)id * table_cols + col_off + i]) : 0.0f);
-    }
-}
-
-extern "C" int tt_side_gate_rows(float* residual, const float* delta, int splits, long long split_stride, const void* w, int w_dtype,
-                                 int hidden, int dim, const void* table, int table_dtype, int vocab, int table_cols, int col_off,
-                                 const int* tokens, int n_tokens, void* out, int out_dtype, unsigned* status, cudaStream_t stream) {
-    if (n_tokens <= 0) return 0;
-    if (col_off < 0 || col_off + dim > table_cols || w_dtype != table_dtype) return (int)cudaErrorInvalidValue;
-    const size_t shared = (size_t)hidden * sizeof(float);
-    if (shared > 48 * 1024) return (int)cudaErrorInvalidValue;
-    if (!delta) splits = 0;
-#define TT_SIDE_ROWS(TA, TW) tt_launch_pdl(side_gate_rows_kernel<TA, TW, TW>, dim3(n_tokens), dim3(256), shared, stream, residual, delta, splits, (size_t)split_stride, (const TW*)w, hidden, dim, (const TW*)table, vocab, table_cols, col_off, tokens, (TA*)out, status)
-    if (out_dtype == TT_F32 && w_dtype == TT_F32) TT_SIDE_ROWS(float, float);
-    else if (out_dtype == TT_F32) TT_SIDE_ROWS(float, __nv_bfloat16);
-    else if (w_dtype == TT_F32) TT_SIDE_ROWS(__nv_bfloat16, float);
-    else TT_SIDE_ROWS(__nv_bfloat16, __nv_bfloat16);
-#undef TT_SIDE_ROWS
-    TT_LAUNCH_CHECK();
-}

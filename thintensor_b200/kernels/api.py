@@ -1063,34 +1063,6 @@ def token_side_gate(x: torch.Tensor, table: torch.Tensor, col_off: int, tokens: 
               _ptr(out), dtype_code(out.dtype), _ptr(status), _stream()), "token_side_gate")
 
 
-SIDE_ROWS_MAX_HIDDEN = 12288        # a row staged in 48 KB of shared memory
-
-
-def side_gate_rows(residual: torch.Tensor, delta: torch.Tensor | None, w: torch.Tensor, table: torch.Tensor, col_off: int, tokens: torch.Tensor,
-                   out: torch.Tensor, status: torch.Tensor) -> None:
-    """:func:`add_narrow`, the gate's product and :func:`token_side_gate` in one kernel, a block per token, for steps of few
-    tokens: ``residual += sum of delta's slices``; ``out[t, i] = gelu_tanh(w[i] . x_t) * table[tokens[t], col_off + i]`` with x the
-    stream's row narrowed to ``out``'s dtype and float32 sums.  ``w`` ``[dim, hidden]`` and ``table`` share a dtype."""
-    _need(residual, torch.float32, "residual")
-    _need(tokens, torch.int32, "tokens")
-    n, hidden = residual.shape
-    dim = w.shape[0]
-    if (not w.is_contiguous() or not table.is_contiguous() or w.shape[1] != hidden or w.dtype != table.dtype or tokens.numel() != n
-            or tuple(out.shape) != (n, dim) or not out.is_contiguous() or hidden > SIDE_ROWS_MAX_HIDDEN):
-        raise KernelError("side_gate_rows: shapes do not fit")
-    if col_off < 0 or col_off + dim > table.shape[1]:
-        raise KernelError("side_gate_rows: the slice lies outside the table's rows")
-    p, splits, stride = c_void_p(0), 0, 0
-    if delta is not None:
-        p, splits, stride, cols = _projection(delta)
-        if tuple(delta.shape[1:]) != (n, hidden):
-            raise KernelError("side_gate_rows: the delta does not fit the stream")
-    fn = _fn("elementwise", "tt_side_gate_rows", [c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int,
-                                                  c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p])
-    _check(fn(_ptr(residual), p, splits, stride, _ptr(w), dtype_code(w.dtype), hidden, dim, _ptr(table), dtype_code(table.dtype), table.shape[0],
-              table.shape[1], col_off, _ptr(tokens), n, _ptr(out), dtype_code(out.dtype), _ptr(status), _stream()), "side_gate_rows")
-
-
 def sigmoid_gate(y: torch.Tensor, gate: torch.Tensor, head_width: int = 0) -> None:
     """In place: y[t, c] *= sigmoid(sum of the float32 slices gate[s, t, c]), or with ``head_width`` > 0 one gate number per
     head, gate[s, t, c // head_width].  ``gate`` may be a range of a wider projection's columns."""

@@ -4,9 +4,8 @@
 ``layers * dim`` long; a layer reads the columns from ``offset`` on).  With x the stream after the layer's last sublayer and
 e the layer's slice of the token's row: ``g = gelu_tanh(W_gate x) * e`` (``W_gate`` is ``[dim, hidden]``), ``y = W_proj g``
 (``[hidden, dim]``), and the stream takes ``y / sqrt(mean(y^2) + eps) * weight``.  The gate reads the stream, not a norm of it,
-so the part first has the layer's pending delta added (one kernel, which also hands the stream on narrowed; a step of few
-tokens does that, the gate's small product and the unit in ONE kernel, a block per token); the norm of y and its addition
-are left to the next norm's kernel (a delta with ``post``).  Sums, the activation and the norm are float32.
+so the part first has the layer's pending delta added (one kernel, which also hands the stream on narrowed); the norm of y
+and its addition are left to the next norm's kernel (a delta with ``post``).  Sums, the activation and the norm are float32.
 """
 from __future__ import annotations
 
@@ -19,7 +18,6 @@ from .linear import Linear
 
 @SIDES.register("token_side")
 class TokenSide(SideInput):
-    ROWS_TOKENS = 32            # steps of up to so many tokens form the gate in one kernel (a block per token re-reads the gate's matrix)
     NAMES = {"table": "side_embed.weight", "gate": "side_gate.weight", "proj": "side_proj.weight", "norm": "side_norm.weight"}
 
     def __init__(self, hidden: int, vocab: int, dim: int, table_cols: int, offset: int, eps: float, names: dict | None = None):
@@ -56,13 +54,8 @@ class TokenSide(SideInput):
     def forward(self, ctx, residual, pending: Delta | None) -> Delta:
         if pending is not None and (pending.post is not None or pending.depth is not None):
             raise RuntimeError("the token side input follows a plain delta")
+        stream = ctx.scratch("side.stream", tuple(residual.shape))
+        api.add_narrow(residual, None if pending is None else pending.tensor, stream)
         gated = ctx.scratch("side.gated", (ctx.n_tokens, self.dim))
-        if (ctx.n_tokens <= self.ROWS_TOKENS and self.hidden <= api.SIDE_ROWS_MAX_HIDDEN and self.gate.weight.dtype == self.table.dtype):
-            # few tokens: the addition, the gate's small product and the unit in one kernel, a block per token
-            api.side_gate_rows(residual, None if pending is None else pending.tensor, self.gate.weight, self.table, self.offset, ctx.tokens,
-                               gated, ctx.status)
-        else:
-            stream = ctx.scratch("side.stream", tuple(residual.shape))
-            api.add_narrow(residual, None if pending is None else pending.tensor, stream)
-            api.token_side_gate(self.gate(ctx, stream, "side.gate"), self.table, self.offset, ctx.tokens, gated, ctx.status)
+        api.token_side_gate(self.gate(ctx, stream, "side.gate"), self.table, self.offset, ctx.tokens, gated, ctx.status)
         return Delta(self.proj(ctx, gated, "side.proj"), post=PostNorm(self.norm, self.eps, 0.0))

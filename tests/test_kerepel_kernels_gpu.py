@@ -77,7 +77,7 @@ def attention_plain(q, keys, values, pos, heads, kv_heads, scale, window, cap, s
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,cap,slope,gate", [
     (4, 1, 64, 64, 72, 50.0, True, "elementwise"), (3, 3, 16, 24, 21, 30.0, True, "elementwise"), (6, 2, 48, 8, 0, 0.0, True, None),
     (2, 2, 20, 36, 64, 5.0, False, "head"), (8, 2, 128, 128, 130, 40.0, True, "elementwise"), (1, 1, 8, 8, 1, 0.0, True, "head"),
-    (5, 5, 32, 32, 65, 20.0, True, None)])
+    (5, 5, 32, 32, 65, 20.0, True, None), (6, 2, 64, 64, 100, 30.0, True, "elementwise"), (14, 2, 128, 128, 0, 45.0, True, "head")])
 def test_attention_marked_keys(dtype, heads, kv_heads, dim, vdim, window, cap, slope, gate):
     """Sequences of unequal lengths, prompts and decoding, through a scrambled table.  In every sequence one key is lined up
     with the last query of head 0: without a window far back or at a block border; with a window just inside the last token's

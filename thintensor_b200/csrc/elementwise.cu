@@ -1155,22 +1155,31 @@ __global__ void sigmoid_gate_kernel(T* __restrict__ y, int cols, const float* __
     y[i] = tt_from_float<T>(tt_to_float(y[i]) / (1.0f + expf(-z)));
 }
 
-// the same for bfloat16 rows of whole 16-byte pieces with a gate number per output number: eight numbers a thread
+// the same for bfloat16 rows of whole 16-byte pieces: eight numbers a thread, with a gate number each (head_width 0) or one
+// for the head they all lie in (head_width a multiple of eight)
 __global__ void sigmoid_gate_vec_kernel(__nv_bfloat16* __restrict__ y, int cols, const float* __restrict__ gate, int splits,
-                                        size_t split_stride, int gate_row, size_t total) {
+                                        size_t split_stride, int gate_row, int head_width, size_t total) {
     tt_pdl_launch_dependents();
     tt_pdl_wait();
     const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (i >= total) return;
     const size_t t = i / cols;
     const int c = (int)(i - t * cols);
-    const float* g = gate + t * (size_t)gate_row + c;
     float z[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) z[e] = 0.0f;
-    for (int s = 0; s < splits; ++s) {
-        const float4 a = __ldg(reinterpret_cast<const float4*>(g + s * split_stride)), b = __ldg(reinterpret_cast<const float4*>(g + s * split_stride + 4));
-        z[0] += a.x; z[1] += a.y; z[2] += a.z; z[3] += a.w; z[4] += b.x; z[5] += b.y; z[6] += b.z; z[7] += b.w;
+    if (head_width > 0) {
+        const float* g = gate + t * (size_t)gate_row + c / head_width;
+        float one = 0.0f;
+        for (int s = 0; s < splits; ++s) one += __ldg(g + s * split_stride);
+#pragma unroll
+        for (int e = 0; e < 8; ++e) z[e] = one;
+    } else {
+        const float* g = gate + t * (size_t)gate_row + c;
+        for (int s = 0; s < splits; ++s) {
+            const float4 a = __ldg(reinterpret_cast<const float4*>(g + s * split_stride)), b = __ldg(reinterpret_cast<const float4*>(g + s * split_stride + 4));
+            z[0] += a.x; z[1] += a.y; z[2] += a.z; z[3] += a.w; z[4] += b.x; z[5] += b.y; z[6] += b.z; z[7] += b.w;
+        }
     }
     uint4 raw = *reinterpret_cast<uint4*>(y + i);
     __nv_bfloat16* v = reinterpret_cast<__nv_bfloat16*>(&raw);
@@ -1184,10 +1193,10 @@ extern "C" int tt_sigmoid_gate(void* y, int dtype, int n_tokens, int cols, const
     const size_t total = (size_t)n_tokens * cols;
     if (total == 0) return 0;
     const int threads = 256;
-    if (dtype == TT_BF16 && head_width <= 0 && cols % 8 == 0 && gate_row % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)y & 15) == 0 &&
-        ((uintptr_t)gate & 15) == 0) {
+    const bool each = head_width <= 0 && gate_row % 4 == 0 && split_stride % 4 == 0 && ((uintptr_t)gate & 15) == 0;
+    if (dtype == TT_BF16 && cols % 8 == 0 && ((uintptr_t)y & 15) == 0 && (each || (head_width > 0 && head_width % 8 == 0))) {
         tt_launch_pdl(sigmoid_gate_vec_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, stream, (__nv_bfloat16*)y, cols,
-                      gate, splits, (size_t)split_stride, gate_row, total);
+                      gate, splits, (size_t)split_stride, gate_row, head_width > 0 ? head_width : 0, total);
         TT_LAUNCH_CHECK();
     }
     const unsigned blocks = (unsigned)((total + threads - 1) / threads);

@@ -108,7 +108,7 @@ def test_yarn_frequencies_against_the_plain_ones():
 
     for rot in ({"dims": 8, "base": 1000.0, "scaling": {"factor": 4.0, "original": 32, "fast": 8.0, "slow": 1.0}},
                 {"dims": 32, "base": 10000.0, "scaling": {"factor": 2.0, "original": 64, "fast": 16.0, "slow": 2.0}},
-                {"dims": 64, "base": 50000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+                {"dims": 64, "base": 25000.0, "scaling": {"factor": 40.0, "original": 4096, "fast": 24.0, "slow": 1.5}},
                 {"dims": 16, "base": 500.0}):
         want, factor = plain_kerepel.yarn_frequencies(rot)
         s = rot.get("scaling")

@@ -367,7 +367,7 @@ def random_config(seed: int) -> dict:
         mixer = {"heads": r.choice([1, 2, 4, 7]), "dim": r.choice([8, 20, 32, 72]), "rot_dim": rot_dim, "vdim": r.choice([6, 16, 34, 64]),
                  "kv_rank": r.choice([8, 24, 56, 136]), "scale": r.choice([0.1, 0.3, 0.05])}
         if r.random() < 0.85:
-            mixer["rot"] = {"dims": rot_dim, "base": r.choice([100.0, 50000.0, 1e6])}
+            mixer["rot"] = {"dims": rot_dim, "base": r.choice([100.0, 30000.0, 1e6])}
             if r.random() < 0.7:
                 mixer["rot"]["scaling"] = {"factor": r.choice([1.0, 2.0, 8.0, 40.0]), "original": r.choice([16, 64, 4096]),
                                            "fast": r.choice([4.0, 32.0]), "slow": r.choice([0.5, 1.0, 2.0])}

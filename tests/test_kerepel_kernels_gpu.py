@@ -75,7 +75,7 @@ def attention_plain(q, keys, values, pos, heads, kv_heads, scale, window, cap, s
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("heads,kv_heads,dim,vdim,window,cap,slope,gate", [
-    (4, 1, 64, 64, 72, 50.0, True, "elementwise"), (3, 3, 16, 24, 21, 30.0, True, "elementwise"), (6, 2, 48, 8, 0, 0.0, True, None),
+    (4, 2, 64, 64, 80, 35.0, True, "elementwise"), (3, 3, 16, 24, 21, 30.0, True, "elementwise"), (6, 2, 48, 8, 0, 0.0, True, None),
     (2, 2, 20, 36, 64, 5.0, False, "head"), (8, 2, 128, 128, 130, 40.0, True, "elementwise"), (1, 1, 8, 8, 1, 0.0, True, "head"),
     (5, 5, 32, 32, 65, 20.0, True, None), (6, 2, 64, 64, 100, 30.0, True, "elementwise"), (14, 2, 128, 128, 0, 45.0, True, "head")])
 def test_attention_marked_keys(dtype, heads, kv_heads, dim, vdim, window, cap, slope, gate):
@@ -242,7 +242,7 @@ def route_plain(z, correction, top, groups, keep, sigmoid, top2, plain_weights):
     return chosen, (w if plain_weights else w / (w.sum() + 1e-20))
 
 
-@pytest.mark.parametrize("experts,top,groups,keep,extra", [(16, 3, 4, 3, 1), (6, 2, 3, 2, 1), (8, 3, 4, 2, 0), (5, 5, 1, 1, 1), (4, 1, 4, 2, 2),
+@pytest.mark.parametrize("experts,top,groups,keep,extra", [(16, 4, 4, 2, 1), (6, 2, 3, 2, 1), (8, 3, 4, 2, 0), (5, 5, 1, 1, 1), (4, 1, 4, 2, 2),
                                                           (64, 6, 8, 4, 0), (12, 4, 12, 5, 1), (9, 2, 3, 3, 0)])
 @pytest.mark.parametrize("sigmoid,top2,plain_weights,corrected", [(True, True, True, True), (True, False, False, False), (False, True, True, True),
                                                                    (False, False, False, False)])
@@ -287,7 +287,7 @@ def test_routing_options(experts, top, groups, keep, extra, sigmoid, top2, plain
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,width,shared,limit,shared_limit,gated", [(4, 24, 16, 1.0, 2.0, True), (3, 10, 0, 0.5, 0.0, False), (6, 8, 12, 0.0, 0.75, False),
+@pytest.mark.parametrize("experts,width,shared,limit,shared_limit,gated", [(4, 24, 16, 1.25, 2.5, True), (3, 10, 0, 0.5, 0.0, False), (6, 8, 12, 0.0, 0.75, False),
                                                                            (1, 33, 7, 7.0, 7.0, True)])
 def test_expert_activation(dtype, experts, width, shared, limit, shared_limit, gated):
     from thintensor_b200.kernels import api
@@ -381,7 +381,7 @@ def rotate_pairs_plain(x, pos, inv_freq, dims, factor):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,dim,rot,vdim,rank,gated", [(4, 64, 16, 64, 96, True), (2, 24, 8, 16, 40, True), (1, 48, 16, 8, 24, False), (3, 20, 6, 12, 18, True),
+@pytest.mark.parametrize("heads,dim,rot,vdim,rank,gated", [(4, 48, 16, 64, 80, True), (2, 24, 8, 16, 40, True), (1, 48, 16, 8, 24, False), (3, 20, 6, 12, 18, True),
                                                           (16, 32, 32, 64, 48, True)])
 def test_latent_attention_with_direct_queries(dtype, heads, dim, rot, vdim, rank, gated):
     """One wide projection [kv latent | key part | queries | head gates] in two slices through the prepare kernel (no query
